@@ -1,0 +1,428 @@
+// Batched baseline-JPEG entropy decode (ITU-T T.81 F.2) for sm_100a.
+//
+// One CTA per image.  The scan has no restart markers in FFCV-written files
+// (ffcv/fields/rgb_image.py:26-34 passes only the quality to cv2.imencode), so parallelism inside
+// an image comes from the self-synchronising property of Huffman codes: the unstuffed bit stream
+// is cut into fixed-length subsequences, every thread decodes its subsequence from a guessed
+// state, and the guesses are repaired by re-decoding from the left neighbour's exit state until
+// no input changes (a Jacobi iteration on a chain whose first link is exact, so it converges in
+// a few rounds in practice and in at most one round per thread in the worst case).  A prefix sum
+// of completed blocks then gives every thread its output position and a last pass writes the
+// coefficients.  DC differences are integrated per component by a block-wide scan.
+//
+// Integer / issue-bound work: tables live in shared memory, no tensor cores.
+#include "kernels.h"
+
+namespace ffcvb {
+
+constexpr int kEntropyThreads = 1024;
+
+__device__ __constant__ uint8_t kZigzagNatural[64] = {
+    0,  1,  8,  16, 9,  2,  3,  10, 17, 24, 32, 25, 18, 11, 4,  5,  12, 19, 26, 33, 40, 48,
+    41, 34, 27, 20, 13, 6,  7,  14, 21, 28, 35, 42, 49, 56, 57, 50, 43, 36, 29, 22, 15, 23,
+    30, 37, 44, 51, 58, 59, 52, 45, 38, 31, 39, 46, 53, 60, 61, 54, 47, 55, 62, 63};
+
+// Exclusive prefix sum over the block; `total` receives the block sum.  s_warp holds 33 ints.
+__device__ __forceinline__ int block_scan_exclusive(int v, int *s_warp, int &total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = lane < nwarps ? s_warp[lane] : 0;
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int t = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += t;
+        }
+        s_warp[lane] = winc - w;
+        if (lane == 31) s_warp[32] = winc;
+    }
+    __syncthreads();
+    int r = inc - v + s_warp[warp];
+    total = s_warp[32];
+    __syncthreads();
+    return r;
+}
+
+// 32 bits of the big-endian bit stream starting at bit p.
+__device__ __forceinline__ uint32_t peek32(const uint32_t *__restrict__ words, uint32_t p) {
+    uint32_t i = p >> 5;
+    uint32_t w0 = __byte_perm(words[i], 0, 0x0123);
+    uint32_t w1 = __byte_perm(words[i + 1], 0, 0x0123);
+    return __funnelshift_l(w1, w0, p & 31);
+}
+
+// Length and symbol of the Huffman code at the top of w.  An invalid code consumes 16 bits and
+// yields symbol 0, so that speculative decoding always makes progress.
+__device__ __forceinline__ void huff_lookup(const HuffTable &t, uint32_t w, int &len, int &sym) {
+    uint32_t e = t.look[w >> 23];
+    if (e) {
+        len = e >> 8;
+        sym = e & 255;
+        return;
+    }
+    int code = w >> 16;
+    len = 16;
+    sym = 0;
+#pragma unroll 1
+    for (int l = 10; l <= 16; l++) {
+        int c = code >> (16 - l);
+        if (c <= t.maxcode[l]) {
+            len = l;
+            sym = t.vals[(t.valoff[l] + c) & 255];
+            return;
+        }
+    }
+}
+
+__device__ __forceinline__ int extend(uint32_t bits, int s) {
+    // bits: the s-bit magnitude field (s >= 1)
+    return bits < (1u << (s - 1)) ? (int)bits - (1 << s) + 1 : (int)bits;
+}
+
+struct Cursor {
+    uint32_t p; // bit position in the unstuffed stream
+    int c;      // block slot inside the MCU
+    int z;      // next zigzag index, 0 = DC expected
+};
+
+__device__ __forceinline__ uint64_t pack(const Cursor &s) {
+    return ((uint64_t)s.p << 32) | ((uint32_t)s.c << 8) | (uint32_t)s.z;
+}
+__device__ __forceinline__ Cursor unpack(uint64_t v) {
+    Cursor s;
+    s.p = (uint32_t)(v >> 32);
+    s.c = (int)((v >> 8) & 0xffffff);
+    s.z = (int)(v & 0xff);
+    return s;
+}
+
+// Decodes symbols from `cur` until its position reaches `end`.  Returns the number of blocks
+// completed.  With WRITE, coefficients go to cf (image base) starting at block `blk`.
+template <bool WRITE>
+__device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, Cursor &cur,
+                                           uint32_t end, int bpm, int luma, int ncomp,
+                                           const HuffTable *s_tab, const uint8_t *s_zz,
+                                           int16_t *__restrict__ cf, uint32_t blk,
+                                           uint32_t nblocks) {
+    int done = 0;
+    uint32_t p = cur.p;
+    int c = cur.c, z = cur.z;
+    while (p < end) {
+        const int comp = (ncomp == 1 || c < luma) ? 0 : c - luma + 1;
+        const HuffTable &t = s_tab[comp * 2 + (z ? 1 : 0)];
+        const uint32_t w = peek32(words, p);
+        int len, sym;
+        huff_lookup(t, w, len, sym);
+        int s;
+        if (z == 0) {
+            s = sym & 15;
+            if (WRITE && blk < nblocks) {
+                int v = s ? extend((w << len) >> (32 - s), s) : 0;
+                cf[(size_t)blk * 64] = (int16_t)v;
+            }
+            z = 1;
+        } else {
+            s = sym & 15;
+            const int r = sym >> 4;
+            if (s == 0) {
+                z = (r == 15) ? z + 16 : 64;
+            } else {
+                z += r;
+                if (WRITE && z < 64 && blk < nblocks) {
+                    int v = extend((w << len) >> (32 - s), s);
+                    cf[(size_t)blk * 64 + s_zz[z]] = (int16_t)v;
+                }
+                z++;
+            }
+        }
+        p += len + s;
+        if (z >= 64) {
+            z = 0;
+            done++;
+            blk++;
+            c = (c + 1 == bpm) ? 0 : c + 1;
+        }
+    }
+    cur.p = p;
+    cur.c = c;
+    cur.z = z;
+    return done;
+}
+
+__global__ void __launch_bounds__(kEntropyThreads)
+entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
+                        const uint8_t *__restrict__ blob, const HuffTable *__restrict__ huff,
+                        uint8_t *__restrict__ clean, int16_t *__restrict__ coef,
+                        int32_t *__restrict__ status, int subseq_bits) {
+    __shared__ HuffTable s_tab[6];
+    __shared__ unsigned long long s_state[kEntropyThreads + 1];
+    __shared__ int s_warp[33];
+    __shared__ uint8_t s_zz[64];
+
+    const int img = list[blockIdx.x];
+    const ImageDesc d = descs[img];
+    const int tid = threadIdx.x;
+    if (d.host_status != 0) {
+        if (tid == 0) status[img] = d.host_status;
+        return;
+    }
+    // ---- tables into shared memory
+    for (int c = 0; c < d.ncomp; c++) {
+        const uint32_t *sd = reinterpret_cast<const uint32_t *>(&huff[d.dc_tab[c]]);
+        const uint32_t *sa = reinterpret_cast<const uint32_t *>(&huff[d.ac_tab[c]]);
+        uint32_t *dd = reinterpret_cast<uint32_t *>(&s_tab[2 * c]);
+        uint32_t *da = reinterpret_cast<uint32_t *>(&s_tab[2 * c + 1]);
+        for (int i = tid; i < (int)(sizeof(HuffTable) / 4); i += kEntropyThreads) {
+            dd[i] = sd[i];
+            da[i] = sa[i];
+        }
+    }
+    if (tid < 64) s_zz[tid] = kZigzagNatural[tid];
+
+    // ---- remove byte stuffing (FF 00 -> FF) into the clean stream
+    const uint8_t *scan = blob + d.payload_off + d.scan_off;
+    uint8_t *cl = clean + d.clean_off;
+    uint32_t clean_len = 0;
+    for (uint32_t base = 0; base < d.scan_len; base += kEntropyThreads * 16) {
+        const uint32_t my = base + tid * 16;
+        uint8_t b[16];
+        uint32_t keep = 0;
+        int prev = (my > 0 && my <= d.scan_len) ? scan[my - 1] : 0;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const uint32_t at = my + i;
+            b[i] = at < d.scan_len ? scan[at] : 0;
+            if (at < d.scan_len && !(b[i] == 0 && prev == 0xFF)) keep |= 1u << i;
+            prev = b[i];
+        }
+        int total;
+        int off = block_scan_exclusive(__popc(keep), s_warp, total);
+        uint8_t *o = cl + clean_len + off;
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (keep & (1u << i)) *o++ = b[i];
+        clean_len += total;
+    }
+    if (tid < 16) cl[clean_len + tid] = 0;
+    __syncthreads();
+
+    const uint32_t *words = reinterpret_cast<const uint32_t *>(cl);
+    const uint32_t total_bits = clean_len * 8;
+    const uint32_t S = (uint32_t)subseq_bits;
+    const int bpm = d.bpm, luma = d.hs * d.vs, ncomp = d.ncomp;
+    int16_t *cf = coef + (size_t)d.block_base * 64;
+
+    Cursor zero = {0, 0, 0};
+    unsigned long long carry = pack(zero);
+    uint32_t blk_base = 0;
+    for (;;) {
+        const uint32_t carry_p = (uint32_t)(carry >> 32);
+        if (carry_p >= total_bits || blk_base >= d.nblocks) break;
+        const uint32_t g = carry_p / S + tid;
+        const uint32_t sub_start = g * S;
+        uint32_t sub_end = sub_start + S;
+        if (sub_end > total_bits) sub_end = total_bits;
+        Cursor guess = {sub_start, 0, 0};
+        s_state[tid] = tid == 0 ? carry : pack(guess);
+        unsigned long long last_in = ~0ull;
+        int my_blocks = 0;
+        __syncthreads();
+        for (int iter = 0; iter <= kEntropyThreads; iter++) {
+            const unsigned long long in = s_state[tid];
+            __syncthreads();
+            int changed = 0;
+            if (in != last_in) {
+                Cursor cur = unpack(in);
+                my_blocks = decode_span<false>(words, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz,
+                                               nullptr, 0, 0);
+                s_state[tid + 1] = pack(cur);
+                last_in = in;
+                changed = 1;
+            }
+            if (!__syncthreads_or(changed)) break;
+        }
+        int chunk_blocks;
+        const int first = block_scan_exclusive(my_blocks, s_warp, chunk_blocks);
+        {
+            Cursor cur = unpack(s_state[tid]);
+            decode_span<true>(words, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
+                              blk_base + (uint32_t)first, d.nblocks);
+        }
+        carry = s_state[kEntropyThreads];
+        blk_base += (uint32_t)chunk_blocks;
+        __syncthreads();
+    }
+    if (tid == 0) status[img] = blk_base >= d.nblocks ? 0 : kErrData;
+    __syncthreads();
+
+    // ---- integrate the DC differences of each component over the scan
+    const int nmcu = d.mcus_x * d.mcus_y;
+    int carry_y = 0, carry_cb = 0, carry_cr = 0;
+    for (int base = 0; base < nmcu; base += kEntropyThreads) {
+        const int m = base + tid;
+        int y[4] = {0, 0, 0, 0}, cb = 0, cr = 0;
+        if (m < nmcu) {
+            int acc = 0;
+            for (int k = 0; k < luma; k++) {
+                acc += cf[((size_t)m * bpm + k) * 64];
+                y[k] = acc;
+            }
+            if (ncomp == 3) {
+                cb = cf[((size_t)m * bpm + luma) * 64];
+                cr = cf[((size_t)m * bpm + luma + 1) * 64];
+            }
+        }
+        int ty, tcb, tcr;
+        const int ey = block_scan_exclusive(y[luma - 1], s_warp, ty);
+        const int ecb = block_scan_exclusive(cb, s_warp, tcb);
+        const int ecr = block_scan_exclusive(cr, s_warp, tcr);
+        if (m < nmcu) {
+            for (int k = 0; k < luma; k++)
+                cf[((size_t)m * bpm + k) * 64] = (int16_t)(carry_y + ey + y[k]);
+            if (ncomp == 3) {
+                cf[((size_t)m * bpm + luma) * 64] = (int16_t)(carry_cb + ecb + cb);
+                cf[((size_t)m * bpm + luma + 1) * 64] = (int16_t)(carry_cr + ecr + cr);
+            }
+        }
+        carry_y += ty;
+        carry_cb += tcb;
+        carry_cr += tcr;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Sequential decoder, one thread per image: the general path for streams with restart markers
+// (DRI != 0), which the parallel kernel does not take.  Reads the stuffed stream directly.
+
+struct ByteReader {
+    const uint8_t *p, *end;
+    uint32_t acc; // left-aligned
+    int n;
+    bool marker;
+};
+
+__device__ __forceinline__ void fill(ByteReader &r) {
+    while (r.n <= 24) {
+        uint32_t b = 0;
+        if (!r.marker && r.p < r.end) {
+            b = *r.p;
+            if (b == 0xFF) {
+                if (r.p + 1 < r.end && r.p[1] == 0) {
+                    r.p += 2;
+                } else {
+                    r.marker = true;
+                    b = 0;
+                }
+            } else {
+                r.p++;
+            }
+        }
+        r.acc |= b << (24 - r.n);
+        r.n += 8;
+    }
+}
+
+__global__ void entropy_sequential_kernel(const ImageDesc *__restrict__ descs,
+                                          const int32_t *__restrict__ list, int n_list,
+                                          const uint8_t *__restrict__ blob,
+                                          const HuffTable *__restrict__ huff,
+                                          int16_t *__restrict__ coef, int32_t *__restrict__ status) {
+    const int li = blockIdx.x * blockDim.x + threadIdx.x;
+    if (li >= n_list) return;
+    const int img = list[li];
+    const ImageDesc &d = descs[img];
+    if (d.host_status != 0) {
+        status[img] = d.host_status;
+        return;
+    }
+    ByteReader r;
+    r.p = blob + d.payload_off + d.scan_off;
+    r.end = r.p + d.scan_len;
+    r.acc = 0;
+    r.n = 0;
+    r.marker = false;
+    int16_t *cf = coef + (size_t)d.block_base * 64;
+    const int luma = d.hs * d.vs, nmcu = d.mcus_x * d.mcus_y;
+    int pred[3] = {0, 0, 0};
+    int restarts_left = d.restart_interval;
+    uint32_t blk = 0;
+    int rc = 0;
+    for (int m = 0; m < nmcu && rc == 0; m++) {
+        if (d.restart_interval && restarts_left == 0) {
+            r.acc = 0;
+            r.n = 0;
+            r.marker = false;
+            while (r.p + 1 < r.end && !(r.p[0] == 0xFF && r.p[1] >= 0xD0 && r.p[1] <= 0xD7)) r.p++;
+            if (r.p + 1 >= r.end) {
+                rc = kErrData;
+                break;
+            }
+            r.p += 2;
+            pred[0] = pred[1] = pred[2] = 0;
+            restarts_left = d.restart_interval;
+        }
+        for (int c = 0; c < d.bpm; c++, blk++) {
+            const int comp = (d.ncomp == 1 || c < luma) ? 0 : c - luma + 1;
+            const HuffTable &dc = huff[d.dc_tab[comp]];
+            const HuffTable &ac = huff[d.ac_tab[comp]];
+            int len, sym;
+            fill(r);
+            huff_lookup(dc, r.acc, len, sym);
+            r.acc <<= len;
+            r.n -= len;
+            int s = sym & 15;
+            if (s) {
+                fill(r);
+                pred[comp] += extend(r.acc >> (32 - s), s);
+                r.acc <<= s;
+                r.n -= s;
+            }
+            cf[(size_t)blk * 64] = (int16_t)pred[comp];
+            for (int z = 1; z < 64;) {
+                fill(r);
+                huff_lookup(ac, r.acc, len, sym);
+                r.acc <<= len;
+                r.n -= len;
+                s = sym & 15;
+                const int run = sym >> 4;
+                if (s == 0) {
+                    if (run != 15) break;
+                    z += 16;
+                    continue;
+                }
+                z += run;
+                fill(r);
+                const int v = extend(r.acc >> (32 - s), s);
+                r.acc <<= s;
+                r.n -= s;
+                if (z > 63) break;
+                cf[(size_t)blk * 64 + kZigzagNatural[z]] = (int16_t)v;
+                z++;
+            }
+        }
+        if (d.restart_interval) restarts_left--;
+    }
+    status[img] = rc;
+}
+
+void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
+                           const int32_t *seq_list, int n_seq, const uint8_t *blob,
+                           const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
+                           int subseq_bits, cudaStream_t stream) {
+    if (n_list > 0)
+        entropy_parallel_kernel<<<n_list, kEntropyThreads, 0, stream>>>(descs, list, blob, huff, clean,
+                                                                        coef, status, subseq_bits);
+    if (n_seq > 0)
+        entropy_sequential_kernel<<<(n_seq + 31) / 32, 32, 0, stream>>>(descs, seq_list, n_seq, blob,
+                                                                        huff, coef, status);
+}
+
+} // namespace ffcvb

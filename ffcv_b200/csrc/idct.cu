@@ -1,0 +1,191 @@
+// Dequantisation + fast integer inverse DCT + chroma upsampling + colour conversion (sm_100a).
+//
+// The arithmetic is the variant TurboJPEG selects for the reference's call
+// (libffcv/libffcv.cpp:104-106, TJFLAG_FASTDCT without TJFLAG_FASTUPSAMPLE): the AAN fast integer
+// IDCT evaluated in wrapping 16-bit lanes with 8-bit constants and truncating shifts, the 3:1
+// triangle ("fancy") chroma upsampler, and the 16.16 fixed-point YCbCr->RGB transform.  These are
+// integer butterflies in registers; they are not a dense contraction and must not be reordered,
+// so no tensor cores.
+#include "kernels.h"
+
+namespace ffcvb {
+
+__device__ __forceinline__ int w16(int v) { return (int)(short)v; }
+__device__ __forceinline__ int mul8(int v, int c) { return w16((v * c) >> 8); }
+
+// One 8-point pass.  Inputs and outputs are sign-extended 16-bit lane values.
+__device__ __forceinline__ void idct8(int &v0, int &v1, int &v2, int &v3, int &v4, int &v5, int &v6,
+                                      int &v7) {
+    int t10 = w16(v0 + v4), t11 = w16(v0 - v4);
+    int t13 = w16(v2 + v6);
+    int t12 = w16(mul8(w16(v2 - v6), 362) - t13);
+    int t0 = w16(t10 + t13), t3 = w16(t10 - t13), t1 = w16(t11 + t12), t2 = w16(t11 - t12);
+    int z13 = w16(v5 + v3), z10 = w16(v5 - v3), z11 = w16(v1 + v7), z12 = w16(v1 - v7);
+    int t7 = w16(z11 + z13);
+    int t11b = mul8(w16(z11 - z13), 362);
+    int z5 = mul8(w16(z10 + z12), 473);
+    int t10b = w16(mul8(z12, 277) - z5);
+    int t12b = w16(mul8(z10, -669) + z5);
+    int t6 = w16(t12b - t7);
+    int t5 = w16(t11b - t6);
+    int t4 = w16(t10b + t5);
+    v0 = w16(t0 + t7);
+    v7 = w16(t0 - t7);
+    v1 = w16(t1 + t6);
+    v6 = w16(t1 - t6);
+    v2 = w16(t2 + t5);
+    v5 = w16(t2 - t5);
+    v4 = w16(t3 + t4);
+    v3 = w16(t3 - t4);
+}
+
+__device__ __forceinline__ int find_image(const ImageDesc *descs, const int32_t *list, int n_list,
+                                          uint32_t blk) {
+    // largest k with descs[list[k]].block_base <= blk (block_base ascends along the list)
+    int lo = 0, hi = n_list - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (descs[list[mid]].block_base <= blk)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    return list[lo];
+}
+
+__global__ void __launch_bounds__(128)
+idct_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list, int n_list,
+            uint32_t total_blocks, const MultTable *__restrict__ mult,
+            const int16_t *__restrict__ coef, uint8_t *__restrict__ planes) {
+    const uint32_t gb = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gb >= total_blocks) return;
+    const ImageDesc &d = descs[find_image(descs, list, n_list, gb)];
+    if (d.host_status != 0) return;
+    const uint32_t b = gb - d.block_base;
+    if (b >= d.nblocks) return;
+    const int luma = d.hs * d.vs;
+    const uint32_t mcu = b / d.bpm;
+    const int slot = (int)(b - mcu * d.bpm);
+    const int my = mcu / d.mcus_x, mx = mcu - my * d.mcus_x;
+    int comp, bx, by, plane_w;
+    if (d.ncomp == 1 || slot < luma) {
+        comp = 0;
+        const int v = slot / d.hs, h = slot - v * d.hs;
+        bx = mx * d.hs + h;
+        by = my * d.vs + v;
+        plane_w = d.mcus_x * d.hs * 8;
+    } else {
+        comp = slot - luma + 1;
+        bx = mx;
+        by = my;
+        plane_w = d.mcus_x * 8;
+    }
+    const int16_t *q = mult[d.q_tab[comp]].m;
+    const int4 *src = reinterpret_cast<const int4 *>(coef + (size_t)gb * 64);
+    int v[8][8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        const int4 cw = src[r];
+        const int4 qw = reinterpret_cast<const int4 *>(q)[r];
+        const int cc[4] = {cw.x, cw.y, cw.z, cw.w};
+        const int qq[4] = {qw.x, qw.y, qw.z, qw.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            v[r][2 * k] = w16((int)(short)(cc[k] & 0xffff) * (int)(short)(qq[k] & 0xffff));
+            v[r][2 * k + 1] = w16((cc[k] >> 16) * (qq[k] >> 16));
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; c++)
+        idct8(v[0][c], v[1][c], v[2][c], v[3][c], v[4][c], v[5][c], v[6][c], v[7][c]);
+    uint8_t *dst = planes + d.plane_off[comp] + (size_t)(by * 8) * plane_w + bx * 8;
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        idct8(v[r][0], v[r][1], v[r][2], v[r][3], v[r][4], v[r][5], v[r][6], v[r][7]);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            int s = v[r][c] >> 5;
+            s = min(127, max(-128, s)) + 128;
+            if (c < 4)
+                lo |= (uint32_t)s << (8 * c);
+            else
+                hi |= (uint32_t)s << (8 * (c - 4));
+        }
+        *reinterpret_cast<uint2 *>(dst + (size_t)r * plane_w) = make_uint2(lo, hi);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ int chroma_sample(const uint8_t *__restrict__ p, int W, int real_w,
+                                             int real_h, int hs, int vs, int x, int y) {
+    if (hs == 1) return p[(size_t)y * W + x];
+    const int cx = x >> 1, cy = vs == 2 ? (y >> 1) : y;
+    const uint8_t *row = p + (size_t)cy * W;
+    if (real_w < 3) return row[cx];
+    if (vs == 1) {
+        const int cur = row[cx];
+        if ((x & 1) == 0) return cx == 0 ? cur : (3 * cur + row[cx - 1] + 1) >> 2;
+        return cx == real_w - 1 ? cur : (3 * cur + row[cx + 1] + 2) >> 2;
+    }
+    int ny = (y & 1) ? cy + 1 : cy - 1;
+    ny = max(0, min(real_h - 1, ny));
+    const uint8_t *far = p + (size_t)ny * W;
+    const int cur = 3 * row[cx] + far[cx];
+    if ((x & 1) == 0) {
+        if (cx == 0) return (cur * 4 + 8) >> 4;
+        return (cur * 3 + 3 * row[cx - 1] + far[cx - 1] + 8) >> 4;
+    }
+    if (cx == real_w - 1) return (cur * 4 + 7) >> 4;
+    return (cur * 3 + 3 * row[cx + 1] + far[cx + 1] + 7) >> 4;
+}
+
+__global__ void __launch_bounds__(256)
+color_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
+             const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb) {
+    const ImageDesc &d = descs[list[blockIdx.y]];
+    if (d.host_status != 0) return;
+    const int W = d.width, H = d.height;
+    const int npix = W * H;
+    const int yw = d.mcus_x * d.hs * 8, cw = d.mcus_x * 8;
+    const int real_w = (W + d.hs - 1) / d.hs, real_h = (H + d.vs - 1) / d.vs;
+    const uint8_t *Y = planes + d.plane_off[0];
+    const uint8_t *Cb = planes + d.plane_off[1];
+    const uint8_t *Cr = planes + d.plane_off[2];
+    uint8_t *out = rgb + d.rgb_off;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < npix; i += gridDim.x * blockDim.x) {
+        const int y = i / W, x = i - y * W;
+        const int lum = Y[(size_t)y * yw + x];
+        int r = lum, g = lum, b = lum;
+        if (d.ncomp == 3) {
+            const int cb = chroma_sample(Cb, cw, real_w, real_h, d.hs, d.vs, x, y) - 128;
+            const int cr = chroma_sample(Cr, cw, real_w, real_h, d.hs, d.vs, x, y) - 128;
+            r = lum + ((91881 * cr + 32768) >> 16);
+            g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
+            b = lum + ((116130 * cb + 32768) >> 16);
+        }
+        out[(size_t)i * 3 + 0] = (uint8_t)min(255, max(0, r));
+        out[(size_t)i * 3 + 1] = (uint8_t)min(255, max(0, g));
+        out[(size_t)i * 3 + 2] = (uint8_t)min(255, max(0, b));
+    }
+}
+
+void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32_t total_blocks,
+                 const MultTable *mult, const int16_t *coef, uint8_t *planes, cudaStream_t stream) {
+    if (total_blocks == 0) return;
+    idct_kernel<<<(total_blocks + 127) / 128, 128, 0, stream>>>(descs, list, n_list, total_blocks, mult,
+                                                               coef, planes);
+}
+
+void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int max_pixels,
+                  const uint8_t *planes, uint8_t *rgb, cudaStream_t stream) {
+    if (n_list == 0) return;
+    int bx = (max_pixels + 256 * 4 - 1) / (256 * 4);
+    if (bx < 1) bx = 1;
+    if (bx > 1024) bx = 1024;
+    dim3 grid(bx, n_list);
+    color_kernel<<<grid, 256, 0, stream>>>(descs, list, planes, rgb);
+}
+
+} // namespace ffcvb

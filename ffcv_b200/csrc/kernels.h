@@ -1,0 +1,42 @@
+// Launch wrappers of the CUDA kernels (sm_100a).  All pointers are device pointers unless noted.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "types.h"
+
+namespace ffcvb {
+
+// Entropy decode of every JPEG sample listed in `list` (indices into descs): unstuffs the scan
+// into `clean`, Huffman-decodes it into quantised coefficients (natural order inside a block,
+// blocks in scan order, DC un-differenced) in `coef`, and records a per-sample status.
+// `subseq_bits` is the length of the subsequences decoded speculatively in parallel (multiple
+// of 32).  `coef` must be zeroed by the caller.
+void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
+                           const int32_t *seq_list, int n_seq, const uint8_t *blob,
+                           const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
+                           int subseq_bits, cudaStream_t stream);
+
+// Dequantise + fast integer IDCT of `total_blocks` blocks into the 8-bit component planes.
+void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32_t total_blocks,
+                 const MultTable *mult, const int16_t *coef, uint8_t *planes, cudaStream_t stream);
+
+// Chroma upsampling (triangle filter) + YCbCr->RGB into packed h*w*3 images in `rgb`.
+void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int max_pixels,
+                  const uint8_t *planes, uint8_t *rgb, cudaStream_t stream);
+
+// Source of the fused kernel.
+struct ResizeSource {
+    const ImageDesc *descs; // per-sample descriptors, or nullptr for a uniform device batch
+    const uint8_t *blob;    // raw payloads live here (descs != nullptr)
+    const uint8_t *rgb;     // decoded JPEG samples live here (descs != nullptr)
+    const uint8_t *uniform; // [n, h, w, 3] uint8 (descs == nullptr)
+    int uniform_h, uniform_w;
+};
+
+// Fused crop + INTER_AREA resize + flip/translate/cutout + lookup-table normalise.
+void launch_resize_augment(const ResizeSource &src, int n, const int32_t *params, int n_params,
+                           const OpList &ops, int resize, int out_h, int out_w, int out_kind,
+                           const void *lut, void *out, const int32_t *status, cudaStream_t stream);
+
+} // namespace ffcvb

@@ -1,0 +1,266 @@
+// Fused crop + INTER_AREA resize + flip / translate / cutout + lookup-table normalise (sm_100a).
+//
+// Replaces, in one pass over the output, the chain the reference runs as separate CPU loops:
+//   cv::resize(roi, dst, INTER_AREA)      libffcv/libffcv.cpp:33-42 (from rgb_image.py:205-208)
+//   RandomHorizontalFlip                  ffcv/transforms/flip.py:31-39
+//   RandomTranslate                       ffcv/transforms/translate.py:35-44
+//   Cutout                                ffcv/transforms/cutout.py:36-46
+//   NormalizeImage (256x3 table gather)   ffcv/transforms/normalize.py:58-109
+// Every output pixel is traced backwards through the augmentations to either a fill colour or a
+// pixel of the resized crop, whose value is computed with OpenCV's INTER_AREA arithmetic:
+//   equal size -> copy; integer factors -> box sum ((s+2)>>2 for 2x2, else
+//   round-half-even(float(s) * float(1/area))); both factors >= 1 -> separable fractional
+//   coverage accumulated in fp32 in source order (no FMA contraction); any factor < 1 -> 2-tap
+//   interpolation on both axes with 11-bit fixed-point weights.
+// HBM-bound byte work: one thread per output pixel, source taps through L1/L2, table in shared
+// memory.
+#include <float.h>
+
+#include "kernels.h"
+
+namespace ffcvb {
+
+enum { kOpFlip = 1, kOpTranslate = 2, kOpCutout = 3 };
+enum { kOutU8 = 0, kOutF16Nhwc = 1, kOutF16Nchw = 2, kOutF32Nhwc = 3, kOutF32Nchw = 4 };
+enum { kCopy = 0, kInteger = 1, kArea = 2, kLinear = 3 };
+
+struct AreaTaps {
+    int first, n;
+    float wl, wm, wr;
+    bool has_l, has_r;
+    __device__ __forceinline__ float weight(int k) const {
+        return (k == 0 && has_l) ? wl : ((k == n - 1 && has_r) ? wr : wm);
+    }
+};
+
+// Source cells covering destination cell d of an axis shrunk by `scale` (>= 1).
+__device__ __forceinline__ AreaTaps area_taps(int d, int ssize, double scale) {
+    AreaTaps t;
+    const double f1 = d * scale, f2 = f1 + scale;
+    const double cell = fmin(scale, ssize - f1);
+    int s1 = (int)ceil(f1), s2 = (int)floor(f2);
+    s2 = min(s2, ssize - 1);
+    s1 = min(s1, s2);
+    t.has_l = (s1 - f1) > 1e-3;
+    t.has_r = (f2 - s2) > 1e-3;
+    t.wl = (float)((s1 - f1) / cell);
+    t.wm = (float)(1.0 / cell);
+    t.wr = (float)(fmin(fmin(f2 - s2, 1.0), cell) / cell);
+    t.first = t.has_l ? s1 - 1 : s1;
+    t.n = (t.has_l ? 1 : 0) + (s2 - s1) + (t.has_r ? 1 : 0);
+    return t;
+}
+
+// Two-tap position and 11-bit weights of destination index d when some axis is enlarged.
+__device__ __forceinline__ void linear_taps(int d, int ssize, double inv, double scale, bool clamp_last,
+                                            int &s, int &w0, int &w1) {
+    s = (int)floor(d * scale);
+    float f = (float)((d + 1) - (s + 1) * inv);
+    f = f <= 0.f ? 0.f : f - floorf(f);
+    if (clamp_last && s >= ssize - 1) {
+        f = 0.f;
+        s = ssize - 1;
+    }
+    w0 = min(32767, __float2int_rn(__fmul_rn(__fsub_rn(1.f, f), 2048.f)));
+    w1 = min(32767, __float2int_rn(__fmul_rn(f, 2048.f)));
+}
+
+__device__ __forceinline__ int sat_round(float v) { return min(255, max(0, __float2int_rn(v))); }
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int n_params, OpList ops,
+                      int resize, int out_h, int out_w, int planar, const OutT *__restrict__ lut,
+                      OutT *__restrict__ out, const int32_t *__restrict__ status) {
+    __shared__ OutT s_lut[768];
+    const int i = blockIdx.y;
+    constexpr bool kU8 = sizeof(OutT) == 1;
+    if (!kU8) {
+        for (int k = threadIdx.x; k < 768; k += blockDim.x) s_lut[k] = lut[k];
+        __syncthreads();
+    }
+    const int pix = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pix >= out_h * out_w) return;
+    const int oy = pix / out_w, ox = pix - oy * out_w;
+
+    // ---- where the sample's pixels are
+    const uint8_t *base;
+    int stride, row0 = 0, img_h, img_w;
+    bool ok = true;
+    if (src.descs) {
+        const ImageDesc &d = src.descs[i];
+        img_h = d.height;
+        img_w = d.width;
+        stride = d.width * 3;
+        if (d.mode == 1) {
+            base = src.blob + d.payload_off;
+            row0 = d.row0;
+        } else {
+            base = src.rgb + d.rgb_off;
+            ok = d.host_status == 0 && (status == nullptr || status[i] == 0);
+        }
+    } else {
+        img_h = src.uniform_h;
+        img_w = src.uniform_w;
+        stride = img_w * 3;
+        base = src.uniform + (size_t)i * img_h * stride;
+    }
+    const int32_t *prm = params + (size_t)i * n_params;
+    int ci = 0, cj = 0, ch = out_h, cw = out_w;
+    if (resize) {
+        ci = prm[0];
+        cj = prm[1];
+        ch = prm[2];
+        cw = prm[3];
+        ok = ok && ch > 0 && cw > 0 && ci >= 0 && cj >= 0 && ci + ch <= img_h && cj + cw <= img_w;
+    } else {
+        ok = ok && img_h == out_h && img_w == out_w;
+    }
+
+    // ---- trace the output pixel back through the augmentations
+    int y = oy, x = ox;
+    bool filled = false;
+    int val[3] = {0, 0, 0};
+    for (int k = ops.n_ops - 1; k >= 0 && !filled; k--) {
+        const int a = prm[4 + 2 * k], b = prm[5 + 2 * k];
+        const int type = ops.type[k], arg = ops.arg[k];
+        if (type == kOpCutout) {
+            filled = y >= a && y < a + arg && x >= b && x < b + arg;
+        } else if (type == kOpTranslate) {
+            y += a - arg;
+            x += b - arg;
+            filled = y < 0 || y >= out_h || x < 0 || x >= out_w;
+        } else if (type == kOpFlip) {
+            if (a) x = out_w - 1 - x;
+        }
+        if (filled) {
+            val[0] = ops.fill[k][0];
+            val[1] = ops.fill[k][1];
+            val[2] = ops.fill[k][2];
+        }
+    }
+
+    if (!filled && ok) {
+        const uint8_t *roi = base + (ptrdiff_t)(ci - row0) * stride + cj * 3;
+        int regime = kCopy;
+        double inv_x = 1, inv_y = 1, sc_x = 1, sc_y = 1;
+        int isx = 1, isy = 1;
+        if (ch != out_h || cw != out_w) {
+            inv_x = (double)out_w / cw;
+            inv_y = (double)out_h / ch;
+            sc_x = 1.0 / inv_x;
+            sc_y = 1.0 / inv_y;
+            if (sc_x >= 1 && sc_y >= 1) {
+                isx = __double2int_rn(sc_x);
+                isy = __double2int_rn(sc_y);
+                regime = (fabs(sc_x - isx) < DBL_EPSILON && fabs(sc_y - isy) < DBL_EPSILON) ? kInteger : kArea;
+            } else {
+                regime = kLinear;
+            }
+        }
+        if (regime == kCopy) {
+            const uint8_t *p = roi + (size_t)y * stride + x * 3;
+            val[0] = p[0];
+            val[1] = p[1];
+            val[2] = p[2];
+        } else if (regime == kInteger) {
+            int s0 = 0, s1 = 0, s2 = 0;
+            for (int j = 0; j < isy; j++) {
+                const uint8_t *p = roi + (size_t)(y * isy + j) * stride + (x * isx) * 3;
+                for (int k = 0; k < isx; k++, p += 3) {
+                    s0 += p[0];
+                    s1 += p[1];
+                    s2 += p[2];
+                }
+            }
+            if (isx == 2 && isy == 2) {
+                val[0] = (s0 + 2) >> 2;
+                val[1] = (s1 + 2) >> 2;
+                val[2] = (s2 + 2) >> 2;
+            } else {
+                const float inv = __fdiv_rn(1.f, (float)(isx * isy));
+                val[0] = sat_round(__fmul_rn((float)s0, inv));
+                val[1] = sat_round(__fmul_rn((float)s1, inv));
+                val[2] = sat_round(__fmul_rn((float)s2, inv));
+            }
+        } else if (regime == kArea) {
+            const AreaTaps tx = area_taps(x, cw, sc_x), ty = area_taps(y, ch, sc_y);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+            for (int j = 0; j < ty.n; j++) {
+                const uint8_t *p = roi + (size_t)(ty.first + j) * stride + tx.first * 3;
+                float r0 = 0.f, r1 = 0.f, r2 = 0.f;
+                for (int k = 0; k < tx.n; k++, p += 3) {
+                    const float w = tx.weight(k);
+                    r0 = __fadd_rn(r0, __fmul_rn((float)p[0], w));
+                    r1 = __fadd_rn(r1, __fmul_rn((float)p[1], w));
+                    r2 = __fadd_rn(r2, __fmul_rn((float)p[2], w));
+                }
+                const float beta = ty.weight(j);
+                if (j == 0) {
+                    a0 = __fmul_rn(beta, r0);
+                    a1 = __fmul_rn(beta, r1);
+                    a2 = __fmul_rn(beta, r2);
+                } else {
+                    a0 = __fadd_rn(a0, __fmul_rn(beta, r0));
+                    a1 = __fadd_rn(a1, __fmul_rn(beta, r1));
+                    a2 = __fadd_rn(a2, __fmul_rn(beta, r2));
+                }
+            }
+            val[0] = sat_round(a0);
+            val[1] = sat_round(a1);
+            val[2] = sat_round(a2);
+        } else {
+            int sx, xa0, xa1, sy, b0, b1;
+            linear_taps(x, cw, inv_x, sc_x, true, sx, xa0, xa1);
+            linear_taps(y, ch, inv_y, sc_y, false, sy, b0, b1);
+            const int sx1 = min(sx + 1, cw - 1);
+            if (sx + 1 >= cw) {
+                xa0 = 2048;
+                xa1 = 0;
+            }
+            const int ry0 = min(sy, ch - 1), ry1 = min(sy + 1, ch - 1);
+            const uint8_t *S0 = roi + (size_t)ry0 * stride, *S1 = roi + (size_t)ry1 * stride;
+#pragma unroll
+            for (int c = 0; c < 3; c++) {
+                const int h0 = S0[3 * sx + c] * xa0 + S0[3 * sx1 + c] * xa1;
+                const int h1 = S1[3 * sx + c] * xa0 + S1[3 * sx1 + c] * xa1;
+                const int v = (((b0 * (h0 >> 4)) >> 16) + ((b1 * (h1 >> 4)) >> 16) + 2) >> 2;
+                val[c] = min(255, max(0, v));
+            }
+        }
+    }
+
+    // ---- normalise (table gather) and store
+    const size_t plane = (size_t)out_h * out_w;
+#pragma unroll
+    for (int c = 0; c < 3; c++) {
+        OutT v;
+        if constexpr (kU8)
+            v = (OutT)val[c];
+        else
+            v = s_lut[val[c] * 3 + c];
+        const size_t o = planar ? ((size_t)i * 3 + c) * plane + pix : ((size_t)i * plane + pix) * 3 + c;
+        out[o] = v;
+    }
+}
+
+void launch_resize_augment(const ResizeSource &src, int n, const int32_t *params, int n_params,
+                           const OpList &ops, int resize, int out_h, int out_w, int out_kind,
+                           const void *lut, void *out, const int32_t *status, cudaStream_t stream) {
+    if (n <= 0) return;
+    dim3 grid((out_h * out_w + 255) / 256, n);
+    const int planar = out_kind == kOutF16Nchw || out_kind == kOutF32Nchw;
+    if (out_kind == kOutU8)
+        resize_augment_kernel<uint8_t><<<grid, 256, 0, stream>>>(src, params, n_params, ops, resize, out_h,
+                                                                 out_w, 0, nullptr, (uint8_t *)out, status);
+    else if (out_kind == kOutF16Nhwc || out_kind == kOutF16Nchw)
+        resize_augment_kernel<uint16_t><<<grid, 256, 0, stream>>>(src, params, n_params, ops, resize, out_h,
+                                                                  out_w, planar, (const uint16_t *)lut,
+                                                                  (uint16_t *)out, status);
+    else
+        resize_augment_kernel<uint32_t><<<grid, 256, 0, stream>>>(src, params, n_params, ops, resize, out_h,
+                                                                  out_w, planar, (const uint32_t *)lut,
+                                                                  (uint32_t *)out, status);
+}
+
+} // namespace ffcvb

@@ -1,0 +1,66 @@
+// Structures shared by the host staging code and the CUDA kernels.  A staged batch is one
+// contiguous blob, identical in pinned host memory and in HBM:
+//   [BatchHeader][ImageDesc x n][HuffTable x n_huff][MultTable x n_mult][params int32][payloads]
+// so one host->device copy moves everything a batch needs.
+#pragma once
+#include <stdint.h>
+
+namespace ffcvb {
+
+constexpr int kMaxComponents = 3;
+constexpr int kPayloadAlign = 16;
+
+// Per-sample work descriptor.
+struct ImageDesc {
+    uint64_t payload_off;  // byte offset of the staged payload inside the blob (16-byte aligned)
+    uint32_t payload_size; // staged bytes
+    uint16_t mode;         // 0 jpg, 1 raw (ffcv/fields/rgb_image.py:21-23)
+    int16_t host_status;   // 0, or a negative code when the host parser rejected the stream
+    uint16_t height, width;
+    uint16_t row0;         // raw: first image row present in the staged payload
+    uint16_t rows;         // raw: number of staged rows
+    // ---- JPEG only ----
+    uint32_t scan_off;     // entropy-coded segment, relative to payload_off
+    uint32_t scan_len;
+    uint8_t ncomp, hs, vs, bpm; // luma sampling factors; blocks per MCU
+    uint16_t mcus_x, mcus_y;
+    uint16_t restart_interval;
+    uint8_t dc_tab[kMaxComponents], ac_tab[kMaxComponents]; // indices into the batch's HuffTable array
+    uint8_t q_tab[kMaxComponents];                          // indices into the batch's MultTable array
+    uint8_t pad0;
+    uint32_t nblocks;      // 8x8 blocks in the scan
+    uint32_t block_base;   // first block of this image in the batch coefficient buffer
+    uint64_t clean_off;    // byte offset of the unstuffed scan in the bitstream scratch (4-aligned)
+    uint64_t plane_off[kMaxComponents]; // byte offsets of the Y/Cb/Cr planes in the plane scratch
+    uint64_t rgb_off;      // byte offset of the decoded h*w*3 image in the RGB scratch
+};
+
+// Canonical Huffman code (ITU-T T.81 Annex C) prepared for table-driven decoding.
+struct HuffTable {
+    uint16_t look[512];  // 9-bit look-ahead: (code length << 8) | symbol; 0 when the code is longer
+    int32_t maxcode[18]; // largest code of each length (left-aligned compare is done by the reader)
+    int32_t valoff[17];  // index of the first symbol of each length minus its first code
+    uint8_t vals[256];
+};
+
+// Dequantisation multipliers of the fast integer IDCT: quantiser step x AAN scale, 2 fraction bits.
+struct MultTable {
+    int16_t m[64];
+};
+
+struct BatchHeader {
+    uint32_t n, n_huff, n_mult, n_params; // n_params = int32 per sample
+    uint64_t desc_off, huff_off, mult_off, params_off, payload_off, total_bytes;
+};
+
+// Augmentation list + output description handed to the fused kernel by value.
+struct OpList {
+    int32_t n_ops;
+    int32_t type[8];
+    int32_t arg[8];
+    uint8_t fill[8][4];
+};
+
+enum : int { kErrFormat = -1, kErrUnsupported = -2, kErrDims = -3, kErrData = -4 };
+
+} // namespace ffcvb

@@ -1,0 +1,194 @@
+"""ctypes binding of ``libffcv_b200.so``.
+
+Plays the role of ``ffcv/libffcv.py:1-56`` in the reference: it loads the native library and
+exposes ``imdecode``, ``resize_crop`` and ``memcpy`` with the reference's Python signatures, plus
+the batch calls (:class:`Context`) the loader uses.  There is no CPU implementation behind this
+module: if the CUDA library is missing or cannot be loaded the import fails.
+"""
+import ctypes
+import os
+from ctypes import (CDLL, POINTER, Structure, c_bool, c_int, c_int32, c_int64, c_uint8, c_uint16,
+                    c_uint32, c_uint64, c_void_p, c_char_p)
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, 'libffcv_b200.so')
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m ffcv_b200._build` (needs nvcc). "
+        "ffcv_b200 has no CPU fallback.")
+
+lib = CDLL(LIB_PATH)
+
+MODE_JPG, MODE_RAW = 0, 1
+OUT_U8_NHWC, OUT_F16_NHWC, OUT_F16_NCHW, OUT_F32_NHWC, OUT_F32_NCHW = range(5)
+OP_FLIP, OP_TRANSLATE, OP_CUTOUT = 1, 2, 3
+MAX_OPS = 8
+
+
+class Op(Structure):
+    _fields_ = [('type', c_int32), ('arg', c_int32), ('fill', c_uint8 * 4)]
+
+
+class Plan(Structure):
+    _fields_ = [('out_h', c_int32), ('out_w', c_int32), ('resize', c_int32), ('out_kind', c_int32),
+                ('n_ops', c_int32), ('ops', Op * MAX_OPS), ('lut_dev', c_void_p)]
+
+
+lib.ffcvb_create.argtypes = [c_int, c_int, c_int, POINTER(c_void_p)]
+lib.ffcvb_create.restype = c_int
+lib.ffcvb_destroy.argtypes = [c_void_p]
+lib.ffcvb_destroy.restype = None
+lib.ffcvb_last_error.argtypes = [c_void_p]
+lib.ffcvb_last_error.restype = c_char_p
+lib.ffcvb_stage_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_int, POINTER(Plan), c_void_p]
+lib.ffcvb_stage_batch.restype = c_int
+lib.ffcvb_submit_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
+lib.ffcvb_submit_batch.restype = c_int
+lib.ffcvb_rerun_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
+lib.ffcvb_rerun_batch.restype = c_int
+lib.ffcvb_staged_bytes.argtypes = [c_void_p, c_int]
+lib.ffcvb_staged_bytes.restype = c_int64
+lib.ffcvb_batch_launches.argtypes = [c_void_p, c_int]
+lib.ffcvb_batch_launches.restype = c_int
+lib.ffcvb_batch_status.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int]
+lib.ffcvb_batch_status.restype = c_int
+lib.ffcvb_transform_device.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                       POINTER(Plan), c_void_p, c_void_p]
+lib.ffcvb_transform_device.restype = c_int
+
+
+def make_plan(out_h, out_w, resize, out_kind, ops=(), lut_dev=0):
+    """ops: sequence of (type, arg, fill) with fill a 3-sequence of ints."""
+    if len(ops) > MAX_OPS:
+        raise ValueError(f'at most {MAX_OPS} fused augmentations')
+    plan = Plan()
+    plan.out_h, plan.out_w = int(out_h), int(out_w)
+    plan.resize = int(bool(resize))
+    plan.out_kind = int(out_kind)
+    plan.n_ops = len(ops)
+    for k, (typ, arg, fill) in enumerate(ops):
+        plan.ops[k].type = int(typ)
+        plan.ops[k].arg = int(arg)
+        for c in range(3):
+            plan.ops[k].fill[c] = int(fill[c]) & 255
+    plan.lut_dev = int(lut_dev) if lut_dev else None
+    return plan
+
+
+class FFCVBError(RuntimeError):
+    pass
+
+
+class Context:
+    """A decode context on one GPU: staging threads, batch slots and device scratch."""
+
+    def __init__(self, device=0, n_slots=1, n_threads=0):
+        handle = c_void_p()
+        rc = lib.ffcvb_create(int(device), int(n_slots), int(n_threads), ctypes.byref(handle))
+        if rc != 0:
+            raise FFCVBError(f'ffcvb_create failed with code {rc} (is a CUDA device visible?)')
+        self._h = handle
+        self.device = int(device)
+        self.n_slots = int(n_slots)
+
+    def _check(self, rc, what):
+        if rc != 0:
+            msg = lib.ffcvb_last_error(self._h)
+            raise FFCVBError(f'{what} failed ({rc}): {msg.decode() if msg else ""}')
+
+    def stage(self, slot, file_base, ptrs, sizes, modes, heights, widths, plan, params):
+        """file_base: integer address (or uint8 array) the sample pointers are relative to."""
+        ptrs = np.ascontiguousarray(ptrs, dtype=np.uint64)
+        sizes = np.ascontiguousarray(sizes, dtype=np.uint64)
+        modes = np.ascontiguousarray(modes, dtype=np.uint8)
+        heights = np.ascontiguousarray(heights, dtype=np.uint16)
+        widths = np.ascontiguousarray(widths, dtype=np.uint16)
+        params = np.ascontiguousarray(params, dtype=np.int32)
+        n = len(ptrs)
+        assert params.shape == (n, 4 + 2 * plan.n_ops), params.shape
+        base = file_base.ctypes.data if isinstance(file_base, np.ndarray) else int(file_base)
+        rc = lib.ffcvb_stage_batch(self._h, slot, base, ptrs.ctypes.data, sizes.ctypes.data,
+                                   modes.ctypes.data, heights.ctypes.data, widths.ctypes.data, n,
+                                   ctypes.byref(plan), params.ctypes.data)
+        self._check(rc, 'ffcvb_stage_batch')
+
+    def submit(self, slot, stream, out_ptr):
+        self._check(lib.ffcvb_submit_batch(self._h, slot, stream or None, out_ptr), 'ffcvb_submit_batch')
+
+    def rerun(self, slot, stream, out_ptr):
+        self._check(lib.ffcvb_rerun_batch(self._h, slot, stream or None, out_ptr), 'ffcvb_rerun_batch')
+
+    def staged_bytes(self, slot):
+        return int(lib.ffcvb_staged_bytes(self._h, slot))
+
+    def launches(self, slot):
+        return int(lib.ffcvb_batch_launches(self._h, slot))
+
+    def status(self, slot, stream, n):
+        st = np.zeros(n, dtype=np.int32)
+        bad = lib.ffcvb_batch_status(self._h, slot, stream or None, st.ctypes.data, n)
+        if bad < 0:
+            self._check(bad, 'ffcvb_batch_status')
+        return st
+
+    def transform_device(self, stream, src_ptr, n, h, w, plan, params, out_ptr):
+        params = np.ascontiguousarray(params, dtype=np.int32)
+        assert params.shape == (n, 4 + 2 * plan.n_ops), params.shape
+        rc = lib.ffcvb_transform_device(self._h, stream or None, src_ptr, n, h, w, ctypes.byref(plan),
+                                        params.ctypes.data, out_ptr)
+        self._check(rc, 'ffcvb_transform_device')
+
+    def close(self):
+        if getattr(self, '_h', None):
+            lib.ffcvb_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---- the reference's single-image calls (ffcv/libffcv.py:22-55), same names and arguments -----
+
+ctypes_resize = lib.resize
+ctypes_resize.argtypes = 11 * [c_int64]
+ctypes_resize.restype = None
+
+
+def resize_crop(source, start_row, end_row, start_col, end_col, destination):
+    ctypes_resize(0, source.ctypes.data, source.shape[0], source.shape[1], start_row, end_row,
+                  start_col, end_col, destination.ctypes.data, destination.shape[0],
+                  destination.shape[1])
+
+
+ctypes_imdecode = lib.imdecode
+ctypes_imdecode.argtypes = [c_void_p, c_uint64, c_uint32, c_uint32, c_void_p, c_uint32, c_uint32,
+                            c_uint32, c_uint32, c_uint32, c_uint32, c_bool, c_bool]
+ctypes_imdecode.restype = c_int
+
+
+def imdecode(source: np.ndarray, dst: np.ndarray, source_height: int, source_width: int,
+             crop_height=None, crop_width=None, offset_x=0, offset_y=0, scale_factor_num=1,
+             scale_factor_denom=1, enable_crop=False, do_flip=False):
+    if crop_height is None:
+        crop_height = source_height
+    if crop_width is None:
+        crop_width = source_width
+    return ctypes_imdecode(source.ctypes.data, source.size, source_height, source_width,
+                           dst.ctypes.data, crop_height, crop_width, offset_x, offset_y,
+                           scale_factor_num, scale_factor_denom, enable_crop, do_flip)
+
+
+ctypes_memcopy = lib.my_memcpy
+ctypes_memcopy.argtypes = [c_void_p, c_void_p, c_uint64]
+ctypes_memcopy.restype = None
+
+
+def memcpy(source: np.ndarray, dest: np.ndarray):
+    return ctypes_memcopy(source.ctypes.data, dest.ctypes.data, source.size * source.itemsize)

@@ -1,0 +1,154 @@
+/*
+ * ffcv_b200 — C ABI of the B200 (sm_100a) decode-and-augment library, libffcv_b200.so.
+ *
+ * It replaces the native half of FFCV's image path: libffcv/libffcv.cpp (`imdecode` ->
+ * tjDecompress2, `resize` -> cv::resize INTER_AREA, `my_memcpy`) together with the per-batch work
+ * of the numba closures in ffcv/fields/rgb_image.py and ffcv/transforms/{flip,translate,cutout,
+ * normalize}.py.  Plain pointers and sizes only; no torch or CUDA types appear in a signature
+ * (a CUDA stream travels as `void *`, i.e. a cudaStream_t / CUstream handle, NULL = default).
+ *
+ * Error convention: every function that can fail returns 0 on success and a negative FFCVB_E_*
+ * code otherwise; nothing throws and no kernel traps.  ffcvb_last_error() gives the message of
+ * the last failure on a context.  Per-sample decode problems (corrupt or unsupported JPEG) do not
+ * fail the batch: they are reported through ffcvb_batch_status().
+ *
+ * Threading: one context per consumer thread.  Calls on one context must not overlap.  Batch
+ * work is asynchronous with respect to the given stream; a slot's host and device buffers may be
+ * reused once work queued on that stream for the slot's previous batch has completed (the caller
+ * fences this with events exactly as ffcv/loader/epoch_iterator.py:96-108,127-129 does).
+ */
+#ifndef FFCV_B200_H
+#define FFCV_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    FFCVB_OK = 0,
+    FFCVB_E_CUDA = -1,     /* a CUDA runtime call failed */
+    FFCVB_E_ARG = -2,      /* invalid argument */
+    FFCVB_E_NOMEM = -3,    /* host or device allocation failed */
+    FFCVB_E_DECODE = -4,   /* JPEG stream could not be decoded (single-image entry points) */
+    FFCVB_E_NODEVICE = -5, /* no usable CUDA device */
+    FFCVB_E_LIMIT = -6     /* a fixed capacity was exceeded */
+};
+
+/* Sample storage modes, ffcv/fields/rgb_image.py:21-23. */
+enum { FFCVB_MODE_JPG = 0, FFCVB_MODE_RAW = 1 };
+
+/* Layout and type of the batch output. */
+enum {
+    FFCVB_OUT_U8_NHWC = 0,  /* uint8  [n, h, w, 3] */
+    FFCVB_OUT_F16_NHWC = 1, /* fp16   [n, h, w, 3], values from the lookup table */
+    FFCVB_OUT_F16_NCHW = 2, /* fp16   [n, 3, h, w] */
+    FFCVB_OUT_F32_NHWC = 3, /* fp32   [n, h, w, 3] */
+    FFCVB_OUT_F32_NCHW = 4  /* fp32   [n, 3, h, w] */
+};
+
+/* Augmentations applied after the decoder, in pipeline order. */
+enum {
+    FFCVB_OP_FLIP = 1,      /* ffcv/transforms/flip.py:31-39       param: (flip?, unused) */
+    FFCVB_OP_TRANSLATE = 2, /* ffcv/transforms/translate.py:35-44  arg = padding, param: (y, x) */
+    FFCVB_OP_CUTOUT = 3     /* ffcv/transforms/cutout.py:36-46     arg = size,    param: (y, x) */
+};
+
+#define FFCVB_MAX_OPS 8
+
+typedef struct {
+    int32_t type;    /* FFCVB_OP_* */
+    int32_t arg;     /* padding (translate) or square size (cutout) */
+    uint8_t fill[4]; /* RGB fill colour, 4th byte unused */
+} ffcvb_op;
+
+/* What one batch call computes.  The per-sample random draws are NOT made here: the caller
+ * samples them (ffcv/fields/rgb_image.py:48-81, flip.py:32, translate.py:40-41, cutout.py:39-42)
+ * and passes them as `params`, one row of 4 + 2 * n_ops int32 per sample:
+ *   [crop_row, crop_col, crop_h, crop_w,  op0_a, op0_b,  op1_a, op1_b, ...]
+ * The crop box is ignored when resize == 0. */
+typedef struct {
+    int32_t out_h, out_w; /* spatial size of every output image */
+    int32_t resize;       /* 0: images pass through at their stored size (SimpleRGBImageDecoder,
+                             rgb_image.py:84-139; every image must be out_h x out_w);
+                             1: crop box + INTER_AREA resize (rgb_image.py:142-217) */
+    int32_t out_kind;     /* FFCVB_OUT_* */
+    int32_t n_ops;
+    ffcvb_op ops[FFCVB_MAX_OPS];
+    const void *lut_dev; /* DEVICE pointer to the 256 x 3 normalisation table of the output type
+                            (ffcv/transforms/normalize.py:42-49); unused for FFCVB_OUT_U8_NHWC */
+} ffcvb_plan;
+
+typedef struct ffcvb_ctx ffcvb_ctx;
+
+/* Creates a context bound to CUDA device `device` with `n_slots` independent batch slots (the
+ * ring of ffcv/loader/epoch_iterator.py:62-68) and `n_threads` host staging threads (<= 0: one
+ * per available core, capped at 32).  Replaces the per-thread TurboJPEG handles of
+ * libffcv/libffcv.cpp:21-31,63-76. */
+int ffcvb_create(int device, int n_slots, int n_threads, ffcvb_ctx **out);
+void ffcvb_destroy(ffcvb_ctx *ctx);
+const char *ffcvb_last_error(const ffcvb_ctx *ctx);
+
+/* Stage one batch: gathers the payload bytes of `n` samples (sample i occupies
+ * file_base[ptrs[i] .. ptrs[i] + sizes[i]), the byte range `memory_read` returns in
+ * ffcv/memory_managers/os_cache.py:55-60) into the slot's pinned buffer with the staging threads,
+ * parses JPEG headers, and lays out the device work.  modes/heights/widths are the per-sample
+ * metadata columns of ffcv/fields/rgb_image.py:301-308.  Raw samples stage only the rows their
+ * crop box touches.  Host-only; does not touch the GPU except to grow buffers. */
+int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const uint64_t *ptrs,
+                      const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
+                      const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params);
+
+/* Queue the staged batch on `stream`: one host->device copy of the staged bytes, then the decode
+ * (entropy decode, dequantise + IDCT, chroma upsample + colour conversion) and the fused
+ * crop/resize/augment/normalise kernels, writing `n` images into `out_dev` (DEVICE pointer,
+ * layout plan.out_kind).  Replaces the prange loop of rgb_image.py:185-210 and the transform
+ * closures after it.  Returns after queueing. */
+int ffcvb_submit_batch(ffcvb_ctx *ctx, int slot, void *stream, void *out_dev);
+
+/* Re-runs the kernels of a batch whose staged bytes an earlier ffcvb_submit_batch on this slot
+ * already copied to the GPU: same work, no host->device copy.  For measuring the rate with inputs
+ * resident in HBM; no counterpart in the reference. */
+int ffcvb_rerun_batch(ffcvb_ctx *ctx, int slot, void *stream, void *out_dev);
+
+/* Bytes the last staged batch of `slot` moves host->device, and how many of this library's
+ * kernels ffcvb_submit_batch launches for it. */
+int64_t ffcvb_staged_bytes(const ffcvb_ctx *ctx, int slot);
+int ffcvb_batch_launches(const ffcvb_ctx *ctx, int slot);
+
+/* After the stream has completed the slot's batch: copies the per-sample status words
+ * (0 = ok, otherwise FFCVB_E_DECODE) into status[0..n).  Returns the number of failed samples.
+ * The reference drops imdecode's return code (rgb_image.py:131,196); this keeps it. */
+int ffcvb_batch_status(ffcvb_ctx *ctx, int slot, void *stream, int32_t *status, int n);
+
+/* Augment + normalise a batch that already sits on the device as uint8 [n, h, w, 3]
+ * (`src_dev`), e.g. the output of an earlier call; params as above (host pointer, crop box
+ * honoured when plan.resize == 1).  Used when a pipeline cannot be fused into one call. */
+int ffcvb_transform_device(ffcvb_ctx *ctx, void *stream, const uint8_t *src_dev, int n, int h,
+                           int w, const ffcvb_plan *plan, const int32_t *params, void *out_dev);
+
+/* ---- single-image entry points with the reference's exact signatures --------------------
+ * Drop-in for the symbols ffcv/libffcv.py:22-55 binds with ctypes.  HOST pointers in and out;
+ * each call copies to the GPU, runs the kernels and copies back, synchronously, on a process-wide
+ * context for the current device.  They exist for parity with the reference ABI; the batch calls
+ * above are the fast path. */
+
+/* libffcv/libffcv.cpp:33-42. */
+void resize(int64_t cresizer, int64_t source_p, int64_t sx, int64_t sy, int64_t start_row,
+            int64_t end_row, int64_t start_col, int64_t end_col, int64_t dest_p, int64_t tx,
+            int64_t ty);
+/* libffcv/libffcv.cpp:53-112.  Returns 0, or -1 as tjDecompress2 does. */
+int imdecode(unsigned char *input_buffer, uint64_t input_size, uint32_t source_height,
+             uint32_t source_width, unsigned char *output_buffer, uint32_t crop_height,
+             uint32_t crop_width, uint32_t offset_x, uint32_t offset_y, uint32_t scale_num,
+             uint32_t scale_denom, bool enable_crop, bool hflip);
+/* libffcv/libffcv.cpp:44-46. */
+void my_memcpy(void *source, void *dst, uint64_t size);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -16,6 +16,7 @@
  *                         11-bit fixed-point weights, horizontal pass in int32 and the vertical
  *                         pass ((b0*(S0>>4))>>16 + (b1*(S1>>4))>>16 + 2) >> 2.
  */
+#include <float.h>
 #include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -64,7 +65,7 @@ static int area_taps(int ssize, int dsize, double scale, AreaTap *tab) {
 
 static void resize_area_general(const uint8_t *src, int sstride, int sh, int sw, uint8_t *dst,
                                 int dh, int dw) {
-    double scx = (double)sw / dw, scy = (double)sh / dh;
+    double scx = 1.0 / ((double)dw / sw), scy = 1.0 / ((double)dh / sh);
     AreaTap *xt = (AreaTap *)malloc(sizeof(AreaTap) * (size_t)(sw + 2 * dw + 2));
     AreaTap *yt = (AreaTap *)malloc(sizeof(AreaTap) * (size_t)(sh + 2 * dh + 2));
     int nx = area_taps(sw, dw, scx, xt), ny = area_taps(sh, dh, scy, yt);
@@ -178,9 +179,13 @@ void oracle_resize_area(const uint8_t *src, int src_cols, int r0, int r1, int c0
         for (int y = 0; y < sh; y++) memcpy(dst + (size_t)y * sw * 3, roi + (size_t)y * sstride, (size_t)sw * 3);
         return;
     }
-    if (sh >= dst_rows && sw >= dst_cols) {
-        if (sh % dst_rows == 0 && sw % dst_cols == 0)
-            resize_area_integer(roi, sstride, sh / dst_rows, sw / dst_cols, dst, dst_rows, dst_cols);
+    /* OpenCV derives the factors as 1 / (dst / src) in double and calls them integer when they
+     * are within DBL_EPSILON of one */
+    double scx = 1.0 / ((double)dst_cols / sw), scy = 1.0 / ((double)dst_rows / sh);
+    if (scx >= 1 && scy >= 1) {
+        long ix = lrint(scx), iy = lrint(scy);
+        if (fabs(scx - ix) < DBL_EPSILON && fabs(scy - iy) < DBL_EPSILON)
+            resize_area_integer(roi, sstride, (int)iy, (int)ix, dst, dst_rows, dst_cols);
         else
             resize_area_general(roi, sstride, sh, sw, dst, dst_rows, dst_cols);
         return;
