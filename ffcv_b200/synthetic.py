@@ -40,3 +40,82 @@ def synth_image(cfg_id, k, short_lo, short_hi, ratio_lo=0.75, ratio_hi=4 / 3, no
     rng = np.random.default_rng([cfg_id, k])
     h, w = synth_shape(rng, short_lo, short_hi, ratio_lo, ratio_hi)
     return synth_content(rng, h, w, noise_sigma), rng
+
+
+# ---------------------------------------------------------------------------------------------
+# The five benchmark configurations as seeded synthetic datasets.
+
+CONFIGS = {
+    # id: image shape law, field arguments, label range
+    0: dict(name='cifar_raw', fixed=(32, 32), field=dict(write_mode='raw'), labels=10, count=50_000),
+    1: dict(name='imagenet_lowres_jpg', short=(200, 256), ratio=(3 / 4, 4 / 3),
+            field=dict(write_mode='jpg', jpeg_quality=90, max_resolution=256), labels=1000, count=100_000),
+    2: dict(name='imagenet_fullres_mix', short=(300, 500), ratio=(3 / 4, 4 / 3),
+            field=dict(write_mode='proportion', compress_probability=0.5, jpeg_quality=90,
+                       max_resolution=500), labels=1000, count=200_000),
+    3: dict(name='imagenet_val_jpg', short=(200, 256), ratio=(3 / 4, 4 / 3),
+            field=dict(write_mode='jpg', jpeg_quality=90, max_resolution=256), labels=1000, count=50_000),
+    4: dict(name='highres_444', short=(1024, 1536), ratio=(3 / 4, 16 / 9),
+            field=dict(write_mode='jpg', jpeg_quality=95), labels=1000, count=20_000, sampling=444),
+}
+
+
+class SyntheticImageDataset:
+    """Indexed dataset of (image, label) for one configuration.  ``__getitem__`` also seeds numpy's
+    global generator from the sample index, which makes the writer's 'proportion' coin
+    (``np.random.rand() < compress_probability``) reproducible."""
+
+    def __init__(self, cfg_id, count=None):
+        self.cfg_id = cfg_id
+        self.cfg = CONFIGS[cfg_id]
+        self.count = self.cfg['count'] if count is None else int(count)
+
+    def __len__(self):
+        return self.count
+
+    def __getitem__(self, k):
+        cfg = self.cfg
+        rng = np.random.default_rng([self.cfg_id, k])
+        if 'fixed' in cfg:
+            h, w = cfg['fixed']
+            img = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+        else:
+            h, w = synth_shape(rng, cfg['short'][0], cfg['short'][1], cfg['ratio'][0], cfg['ratio'][1])
+            img = synth_content(rng, h, w)
+        label = int(rng.integers(0, cfg['labels']))
+        np.random.seed((self.cfg_id * 1_000_003 + k) % (2 ** 32))
+        return img, label
+
+
+def make_field(cfg_id):
+    from .fields import RGBImageField
+    cfg = CONFIGS[cfg_id]
+    if cfg.get('sampling') == 444:
+        import cv2
+
+        class RGBImageField444(RGBImageField):
+            """Same metadata and payload kinds; JPEG written without chroma subsampling."""
+
+            def encode_jpeg(self, image):
+                ok, res = cv2.imencode('.jpg', cv2.cvtColor(image, cv2.COLOR_RGB2BGR),
+                                       [int(cv2.IMWRITE_JPEG_QUALITY), self.jpeg_quality,
+                                        int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR),
+                                        int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444)])
+                if not ok:
+                    raise ValueError("Impossible to encode image in jpeg")
+                return res.reshape(-1)
+        return RGBImageField444(**cfg['field'])
+    return RGBImageField(**cfg['field'])
+
+
+def write_dataset(cfg_id, path, count=None, num_workers=-1, page_size=None):
+    """Writes ``count`` samples (default: the configuration's full size) of a configuration."""
+    from .fields import IntField
+    from .writer import DatasetWriter
+    kwargs = {} if page_size is None else {'page_size': page_size}
+    if cfg_id == 4 and page_size is None:
+        kwargs['page_size'] = 1 << 25  # 4:4:4 q95 images of ~2-4 MB: 32 MiB pages waste less
+    writer = DatasetWriter(path, {'image': make_field(cfg_id), 'label': IntField()},
+                           num_workers=num_workers, **kwargs)
+    writer.from_indexed_dataset(SyntheticImageDataset(cfg_id, count), chunksize=16)
+    return path
