@@ -112,9 +112,11 @@ struct Slot {
     int n = 0, n_jpeg = 0, n_par = 0, n_seq = 0, max_pixels = 0, subseq_bits = 512;
     uint64_t jpeg_list_off = 0, par_list_off = 0, seq_list_off = 0;
     uint32_t total_blocks = 0;
-    size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0;
+    size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes = 0, raw_bytes = 0, jpeg_bytes = 0;
     bool staged = false;
     std::vector<JpegHeader> headers;
+    cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool timed = false; // events of the last run are valid
 };
 
 struct AuxBuf {
@@ -134,6 +136,7 @@ struct ffcvb_ctx {
     std::string err;
     AuxBuf aux[4];
     int aux_next = 0;
+    bool profile = false;
     DevBuf one_src, one_dst; // single-image entry points
 };
 
@@ -258,6 +261,8 @@ void ffcvb_destroy(ffcvb_ctx *ctx) {
         if (s.host) cudaFreeHost(s.host);
         for (DevBuf *b : {&s.blob, &s.clean, &s.coef, &s.planes, &s.rgb, &s.status})
             if (b->p) cudaFree(b->p);
+        for (auto &e : s.ev)
+            if (e) cudaEventDestroy(e);
     }
     for (auto &a : ctx->aux) {
         if (a.dev.p) cudaFree(a.dev.p);
@@ -464,6 +469,15 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.plane_bytes = plane_bytes;
     s.rgb_bytes = rgb_bytes;
     s.subseq_bits = pick_subseq_bits(scan_bytes_par, s.n_par);
+    s.scan_bytes = s.raw_bytes = s.jpeg_bytes = 0;
+    for (int i = 0; i < n; i++) {
+        if (descs[i].mode == FFCVB_MODE_JPG) {
+            s.jpeg_bytes += descs[i].payload_size;
+            if (descs[i].host_status == 0) s.scan_bytes += descs[i].scan_len;
+        } else {
+            s.raw_bytes += descs[i].payload_size;
+        }
+    }
     s.staged = true;
     return FFCVB_OK;
 }
@@ -471,7 +485,15 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
 static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bool copy) {
     const BatchHeader &hd = s.hdr;
     uint8_t *blob = (uint8_t *)s.blob.p;
+    const bool prof = ctx->profile;
+    s.timed = false;
+    if (prof) {
+        for (auto &e : s.ev)
+            if (!e) CU(cudaEventCreate(&e));
+        CU(cudaEventRecord(s.ev[0], st));
+    }
     if (copy) CU(cudaMemcpyAsync(blob, s.host, hd.total_bytes, cudaMemcpyHostToDevice, st));
+    if (prof) CU(cudaEventRecord(s.ev[1], st));
     const ImageDesc *descs = reinterpret_cast<const ImageDesc *>(blob + hd.desc_off);
     const HuffTable *huff = reinterpret_cast<const HuffTable *>(blob + hd.huff_off);
     const MultTable *mult = reinterpret_cast<const MultTable *>(blob + hd.mult_off);
@@ -485,9 +507,14 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         if (s.total_blocks) CU(cudaMemsetAsync(s.coef.p, 0, (size_t)s.total_blocks * 128, st));
         launch_entropy_decode(descs, pl, s.n_par, sl, s.n_seq, blob, huff, (uint8_t *)s.clean.p,
                               (int16_t *)s.coef.p, status, s.subseq_bits, st);
+        if (prof) CU(cudaEventRecord(s.ev[2], st));
         launch_idct(descs, jl, s.n_jpeg, s.total_blocks, mult, (const int16_t *)s.coef.p,
                     (uint8_t *)s.planes.p, st);
+        if (prof) CU(cudaEventRecord(s.ev[3], st));
         launch_color(descs, jl, s.n_jpeg, s.max_pixels, (const uint8_t *)s.planes.p, (uint8_t *)s.rgb.p, st);
+        if (prof) CU(cudaEventRecord(s.ev[4], st));
+    } else if (prof) {
+        for (int k = 2; k <= 4; k++) CU(cudaEventRecord(s.ev[k], st));
     }
     ResizeSource src{};
     src.descs = descs;
@@ -496,6 +523,28 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
     launch_resize_augment(src, s.n, params, (int)hd.n_params, make_oplist(s.plan), s.plan.resize,
                           s.plan.out_h, s.plan.out_w, s.plan.out_kind, s.plan.lut_dev, out_dev, status, st);
     CU(cudaGetLastError());
+    if (prof) {
+        CU(cudaEventRecord(s.ev[5], st));
+        s.timed = true;
+    }
+    return FFCVB_OK;
+}
+
+int ffcvb_set_profiling(ffcvb_ctx *ctx, int enabled) {
+    if (!ctx) return FFCVB_E_ARG;
+    ctx->profile = enabled != 0;
+    return FFCVB_OK;
+}
+
+int ffcvb_batch_times(ffcvb_ctx *ctx, int slot, float *ms) {
+    if (!ctx) return FFCVB_E_ARG;
+    if (slot < 0 || slot >= (int)ctx->slots.size() || !ms)
+        return fail(ctx, FFCVB_E_ARG, "ffcvb_batch_times: bad argument");
+    Slot &s = ctx->slots[slot];
+    if (!s.timed) return fail(ctx, FFCVB_E_ARG, "ffcvb_batch_times: slot %d was not run with profiling on", slot);
+    CU(cudaSetDevice(ctx->device));
+    CU(cudaEventSynchronize(s.ev[5]));
+    for (int k = 0; k < 5; k++) CU(cudaEventElapsedTime(&ms[k], s.ev[k], s.ev[k + 1]));
     return FFCVB_OK;
 }
 
@@ -524,6 +573,20 @@ int ffcvb_rerun_batch(ffcvb_ctx *ctx, int slot, void *stream, void *out_dev) {
 int64_t ffcvb_staged_bytes(const ffcvb_ctx *ctx, int slot) {
     if (!ctx || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return -1;
     return (int64_t)ctx->slots[slot].hdr.total_bytes;
+}
+
+int ffcvb_batch_info(const ffcvb_ctx *ctx, int slot, int64_t *info) {
+    if (!ctx || !info || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return FFCVB_E_ARG;
+    const Slot &s = ctx->slots[slot];
+    info[0] = s.n;
+    info[1] = s.n_jpeg;
+    info[2] = s.total_blocks;
+    info[3] = (int64_t)s.scan_bytes;
+    info[4] = (int64_t)s.plane_bytes;
+    info[5] = (int64_t)s.rgb_bytes;
+    info[6] = (int64_t)s.raw_bytes;
+    info[7] = (int64_t)s.jpeg_bytes;
+    return FFCVB_OK;
 }
 
 int ffcvb_batch_launches(const ffcvb_ctx *ctx, int slot) {

@@ -50,8 +50,14 @@ lib.ffcvb_submit_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_submit_batch.restype = c_int
 lib.ffcvb_rerun_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_rerun_batch.restype = c_int
+lib.ffcvb_set_profiling.argtypes = [c_void_p, c_int]
+lib.ffcvb_set_profiling.restype = c_int
+lib.ffcvb_batch_times.argtypes = [c_void_p, c_int, c_void_p]
+lib.ffcvb_batch_times.restype = c_int
 lib.ffcvb_staged_bytes.argtypes = [c_void_p, c_int]
 lib.ffcvb_staged_bytes.restype = c_int64
+lib.ffcvb_batch_info.argtypes = [c_void_p, c_int, c_void_p]
+lib.ffcvb_batch_info.restype = c_int
 lib.ffcvb_batch_launches.argtypes = [c_void_p, c_int]
 lib.ffcvb_batch_launches.restype = c_int
 lib.ffcvb_batch_status.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int]
@@ -122,8 +128,23 @@ class Context:
     def rerun(self, slot, stream, out_ptr):
         self._check(lib.ffcvb_rerun_batch(self._h, slot, stream or None, out_ptr), 'ffcvb_rerun_batch')
 
+    def set_profiling(self, enabled):
+        self._check(lib.ffcvb_set_profiling(self._h, int(bool(enabled))), 'ffcvb_set_profiling')
+
+    def batch_times(self, slot):
+        """Milliseconds of (h2d copy, entropy decode, idct, colour, resize) of the slot's last run."""
+        ms = np.zeros(5, dtype=np.float32)
+        self._check(lib.ffcvb_batch_times(self._h, slot, ms.ctypes.data), 'ffcvb_batch_times')
+        return ms
+
     def staged_bytes(self, slot):
         return int(lib.ffcvb_staged_bytes(self._h, slot))
+
+    def batch_info(self, slot):
+        info = np.zeros(8, dtype=np.int64)
+        self._check(lib.ffcvb_batch_info(self._h, slot, info.ctypes.data), 'ffcvb_batch_info')
+        keys = ('n', 'n_jpeg', 'blocks', 'scan_bytes', 'plane_bytes', 'rgb_bytes', 'raw_bytes', 'jpeg_bytes')
+        return dict(zip(keys, (int(v) for v in info)))
 
     def launches(self, slot):
         return int(lib.ffcvb_batch_launches(self._h, slot))

@@ -61,6 +61,8 @@ class EpochIterator(Thread):
             if self.is_cuda:
                 ch.cuda.set_device(self.device)
             for b_ix, ixes in enumerate(self.batches):
+                if self.terminate_event.is_set():
+                    return
                 result = self.run_pipeline(b_ix, ixes, slot, events[slot])
                 item = (slot, result)
                 while True:
@@ -120,6 +122,13 @@ class EpochIterator(Thread):
 
     def __iter__(self):
         return self
+
+    def retire(self):
+        """Stops the worker (it finishes the batch it is on) and waits for it: the slot ring is
+        shared by the epochs of a loader, so two workers must never run at once."""
+        self.close()
+        if self.is_alive():
+            self.join()
 
     def close(self):
         self.terminate_event.set()

@@ -147,6 +147,7 @@ class Loader:
         self._streams = None
         self._buffers = None
         self._slot_done = None
+        self._live_iterator = None
         self.graph = None
         self.generate_code()
         self.first_traversal_order = self.next_traversal_order()
@@ -187,9 +188,12 @@ class Loader:
         selected_order = order[:len(self) * self.batch_size]
         epoch = self.next_epoch
         self.next_epoch += 1
+        if self._live_iterator is not None:
+            self._live_iterator.retire()
         if self.graph is None or self.recompile:
             self.generate_code()
-        return EpochIterator(self, selected_order, epoch)
+        self._live_iterator = EpochIterator(self, selected_order, epoch)
+        return self._live_iterator
 
     def filter(self, field_name: str, condition: Callable[[Any], bool]) -> 'Loader':
         new_args = {**self._args}

@@ -114,8 +114,6 @@ class ToTorchImage(Operation):
         return replace(previous_state, shape=(C, H, W), dtype=new_type), alloc
 
     def fuse(self, plan) -> bool:
-        if plan.sealed and not self.channels_last:
-            return False  # the table output was already laid out NHWC
         return plan.set_torch_image(self.channels_last)
 
 

@@ -114,9 +114,21 @@ int ffcvb_submit_batch(ffcvb_ctx *ctx, int slot, void *stream, void *out_dev);
  * resident in HBM; no counterpart in the reference. */
 int ffcvb_rerun_batch(ffcvb_ctx *ctx, int slot, void *stream, void *out_dev);
 
+/* With profiling enabled every batch run also records CUDA events between its stages on the
+ * batch's stream; ffcvb_batch_times waits for the slot's last run and returns the elapsed
+ * milliseconds of ms[0] host->device copy, ms[1] entropy decode (with its memsets), ms[2]
+ * dequantise + IDCT, ms[3] upsample + colour conversion, ms[4] fused resize/augment/normalise.
+ * No counterpart in the reference. */
+int ffcvb_set_profiling(ffcvb_ctx *ctx, int enabled);
+int ffcvb_batch_times(ffcvb_ctx *ctx, int slot, float *ms);
+
 /* Bytes the last staged batch of `slot` moves host->device, and how many of this library's
  * kernels ffcvb_submit_batch launches for it. */
 int64_t ffcvb_staged_bytes(const ffcvb_ctx *ctx, int slot);
+/* Sizes of the slot's staged batch, for bandwidth accounting: info[0] samples, [1] JPEG samples,
+ * [2] 8x8 blocks, [3] entropy-coded bytes, [4] component-plane bytes, [5] decoded RGB bytes,
+ * [6] staged raw-pixel bytes, [7] staged JPEG bytes. */
+int ffcvb_batch_info(const ffcvb_ctx *ctx, int slot, int64_t *info);
 int ffcvb_batch_launches(const ffcvb_ctx *ctx, int slot);
 
 /* After the stream has completed the slot's batch: copies the per-sample status words

@@ -175,8 +175,8 @@ def test_corrupt_jpeg_is_reported_not_fatal(datasets, tmp_path):
     row = int(np.where(r.alloc_table['ptr'] == md['data_ptr'][3])[0][0])
     with open(path, 'r+b') as fp:
         # halve the recorded size of sample 3 (its entropy data runs out), destroy sample 5's header
-        entry = np.array(r.alloc_table[row])
-        entry['size'] = int(entry['size']) // 2
+        entry = r.alloc_table[row:row + 1].copy()
+        entry['size'] = int(entry['size'][0]) // 2
         fp.seek(int(r.header['alloc_table_ptr']) + row * r.alloc_table.dtype.itemsize)
         fp.write(entry.tobytes())
         fp.seek(int(md['data_ptr'][5]))
