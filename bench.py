@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument('--images', type=int, default=4096, help='distinct images in the synthetic dataset')
     ap.add_argument('--workers', type=int, default=0, help='host staging threads per rank (0: cores / ranks)')
     ap.add_argument('--batches-ahead', type=int, default=3)
+    ap.add_argument('--no-cpu-baseline', action='store_true', help='skip the CPU oracle leg (profiling runs)')
     return ap.parse_args()
 
 
@@ -342,7 +343,7 @@ def main_ours(args):
                          'gbs': path_bytes / (total_kernel_ms * 1e-3) / 1e9}}
 
     cpu = None
-    if world == 1:
+    if world == 1 and not args.no_cpu_baseline:
         threads = cores
         batches = oracle_batches(path, 0, 6)
         run_oracle(batches[:1], threads)
