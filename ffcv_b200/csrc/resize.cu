@@ -12,8 +12,9 @@
 //   round-half-even(float(s) * float(1/area))); both factors >= 1 -> separable fractional
 //   coverage accumulated in fp32 in source order (no FMA contraction); any factor < 1 -> 2-tap
 //   interpolation on both axes with 11-bit fixed-point weights.
-// HBM-bound byte work: one thread per output pixel, source taps through L1/L2, table in shared
-// memory.
+// HBM-bound byte work: one CTA per (sample, band of output rows); tap positions and weights are
+// computed once per CTA into shared memory, source taps go through L1/L2, the normalised tile is
+// assembled in shared memory and leaves with coalesced 16-byte stores.
 #include <float.h>
 
 #include "kernels.h"
@@ -67,21 +68,62 @@ __device__ __forceinline__ void linear_taps(int d, int ssize, double inv, double
 
 __device__ __forceinline__ int sat_round(float v) { return min(255, max(0, __float2int_rn(v))); }
 
+// Per-axis tap tables in shared memory, computed once per CTA (double-precision position
+// arithmetic as OpenCV does it, then only fp32 / integer work per pixel).
+struct TapTables {
+    int *first;  // first source index (area) / source index (linear)
+    int *count;  // area: taps | has_l << 16 | has_r << 17; linear: w0 << 16 | w1
+    float *wl, *wm, *wr;
+};
+
+__device__ __forceinline__ void fill_taps(const TapTables &t, int k, int d, int regime, int ssize, double inv,
+                                          double scale, bool clamp_last) {
+    if (regime == kArea) {
+        const AreaTaps a = area_taps(d, ssize, scale);
+        t.first[k] = a.first;
+        t.count[k] = a.n | (a.has_l ? 1 << 16 : 0) | (a.has_r ? 1 << 17 : 0);
+        t.wl[k] = a.wl;
+        t.wm[k] = a.wm;
+        t.wr[k] = a.wr;
+    } else if (regime == kLinear) {
+        int s, w0, w1;
+        linear_taps(d, ssize, inv, scale, clamp_last, s, w0, w1);
+        if (clamp_last && s + 1 >= ssize) {
+            w0 = 2048;
+            w1 = 0;
+        }
+        t.first[k] = s;
+        t.count[k] = (w0 << 16) | w1;
+    }
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int n_params, OpList ops,
-                      int resize, int out_h, int out_w, int planar, const OutT *__restrict__ lut,
-                      OutT *__restrict__ out, const int32_t *__restrict__ status) {
-    __shared__ OutT s_lut[768];
-    const int i = blockIdx.y;
+                      int resize, int out_h, int out_w, int band_rows, int planar,
+                      const OutT *__restrict__ lut, OutT *__restrict__ out,
+                      const int32_t *__restrict__ status) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
     constexpr bool kU8 = sizeof(OutT) == 1;
-    if (!kU8) {
+    // shared layout: [out tile][lut][x taps (5 arrays of out_w)][y taps (5 arrays of ny)]
+    const int band0 = blockIdx.x * band_rows;
+    const int rows = min(band_rows, out_h - band0);
+    const int tile_elems = band_rows * out_w * 3;
+    OutT *s_out = reinterpret_cast<OutT *>(s_raw);
+    size_t off = ((size_t)tile_elems * sizeof(OutT) + 15) & ~(size_t)15;
+    OutT *s_lut = reinterpret_cast<OutT *>(s_raw + off);
+    off += (768 * sizeof(OutT) + 15) & ~(size_t)15;
+    // y taps are indexed by the row of the resized crop (a translation can move a band anywhere)
+    int *ibase = reinterpret_cast<int *>(s_raw + off);
+    TapTables tx{ibase, ibase + out_w, reinterpret_cast<float *>(ibase + 2 * out_w),
+                 reinterpret_cast<float *>(ibase + 3 * out_w), reinterpret_cast<float *>(ibase + 4 * out_w)};
+    int *jbase = ibase + 5 * out_w;
+    TapTables ty{jbase, jbase + out_h, reinterpret_cast<float *>(jbase + 2 * out_h),
+                 reinterpret_cast<float *>(jbase + 3 * out_h), reinterpret_cast<float *>(jbase + 4 * out_h)};
+
+    const int i = blockIdx.y;
+    if (!kU8)
         for (int k = threadIdx.x; k < 768; k += blockDim.x) s_lut[k] = lut[k];
-        __syncthreads();
-    }
-    const int pix = blockIdx.x * blockDim.x + threadIdx.x;
-    if (pix >= out_h * out_w) return;
-    const int oy = pix / out_w, ox = pix - oy * out_w;
 
     // ---- where the sample's pixels are
     const uint8_t *base;
@@ -95,6 +137,7 @@ resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int 
         if (d.mode == 1) {
             base = src.blob + d.payload_off;
             row0 = d.row0;
+            ok = d.host_status == 0;
         } else {
             base = src.rgb + d.rgb_off;
             ok = d.host_status == 0 && (status == nullptr || status[i] == 0);
@@ -116,151 +159,188 @@ resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int 
     } else {
         ok = ok && img_h == out_h && img_w == out_w;
     }
-
-    // ---- trace the output pixel back through the augmentations
-    int y = oy, x = ox;
-    bool filled = false;
-    int val[3] = {0, 0, 0};
-    for (int k = ops.n_ops - 1; k >= 0 && !filled; k--) {
-        const int a = prm[4 + 2 * k], b = prm[5 + 2 * k];
-        const int type = ops.type[k], arg = ops.arg[k];
-        if (type == kOpCutout) {
-            filled = y >= a && y < a + arg && x >= b && x < b + arg;
-        } else if (type == kOpTranslate) {
-            y += a - arg;
-            x += b - arg;
-            filled = y < 0 || y >= out_h || x < 0 || x >= out_w;
-        } else if (type == kOpFlip) {
-            if (a) x = out_w - 1 - x;
-        }
-        if (filled) {
-            val[0] = ops.fill[k][0];
-            val[1] = ops.fill[k][1];
-            val[2] = ops.fill[k][2];
-        }
-    }
-
-    if (!filled && ok) {
-        const uint8_t *roi = base + (ptrdiff_t)(ci - row0) * stride + cj * 3;
-        int regime = kCopy;
-        double inv_x = 1, inv_y = 1, sc_x = 1, sc_y = 1;
-        int isx = 1, isy = 1;
-        if (ch != out_h || cw != out_w) {
-            inv_x = (double)out_w / cw;
-            inv_y = (double)out_h / ch;
-            sc_x = 1.0 / inv_x;
-            sc_y = 1.0 / inv_y;
-            if (sc_x >= 1 && sc_y >= 1) {
-                isx = __double2int_rn(sc_x);
-                isy = __double2int_rn(sc_y);
-                regime = (fabs(sc_x - isx) < DBL_EPSILON && fabs(sc_y - isy) < DBL_EPSILON) ? kInteger : kArea;
-            } else {
-                regime = kLinear;
-            }
-        }
-        if (regime == kCopy) {
-            const uint8_t *p = roi + (size_t)y * stride + x * 3;
-            val[0] = p[0];
-            val[1] = p[1];
-            val[2] = p[2];
-        } else if (regime == kInteger) {
-            int s0 = 0, s1 = 0, s2 = 0;
-            for (int j = 0; j < isy; j++) {
-                const uint8_t *p = roi + (size_t)(y * isy + j) * stride + (x * isx) * 3;
-                for (int k = 0; k < isx; k++, p += 3) {
-                    s0 += p[0];
-                    s1 += p[1];
-                    s2 += p[2];
-                }
-            }
-            if (isx == 2 && isy == 2) {
-                val[0] = (s0 + 2) >> 2;
-                val[1] = (s1 + 2) >> 2;
-                val[2] = (s2 + 2) >> 2;
-            } else {
-                const float inv = __fdiv_rn(1.f, (float)(isx * isy));
-                val[0] = sat_round(__fmul_rn((float)s0, inv));
-                val[1] = sat_round(__fmul_rn((float)s1, inv));
-                val[2] = sat_round(__fmul_rn((float)s2, inv));
-            }
-        } else if (regime == kArea) {
-            const AreaTaps tx = area_taps(x, cw, sc_x), ty = area_taps(y, ch, sc_y);
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f;
-            for (int j = 0; j < ty.n; j++) {
-                const uint8_t *p = roi + (size_t)(ty.first + j) * stride + tx.first * 3;
-                float r0 = 0.f, r1 = 0.f, r2 = 0.f;
-                for (int k = 0; k < tx.n; k++, p += 3) {
-                    const float w = tx.weight(k);
-                    r0 = __fadd_rn(r0, __fmul_rn((float)p[0], w));
-                    r1 = __fadd_rn(r1, __fmul_rn((float)p[1], w));
-                    r2 = __fadd_rn(r2, __fmul_rn((float)p[2], w));
-                }
-                const float beta = ty.weight(j);
-                if (j == 0) {
-                    a0 = __fmul_rn(beta, r0);
-                    a1 = __fmul_rn(beta, r1);
-                    a2 = __fmul_rn(beta, r2);
-                } else {
-                    a0 = __fadd_rn(a0, __fmul_rn(beta, r0));
-                    a1 = __fadd_rn(a1, __fmul_rn(beta, r1));
-                    a2 = __fadd_rn(a2, __fmul_rn(beta, r2));
-                }
-            }
-            val[0] = sat_round(a0);
-            val[1] = sat_round(a1);
-            val[2] = sat_round(a2);
+    int regime = kCopy;
+    double inv_x = 1, inv_y = 1, sc_x = 1, sc_y = 1;
+    int isx = 1, isy = 1;
+    if (ok && (ch != out_h || cw != out_w)) {
+        inv_x = (double)out_w / cw;
+        inv_y = (double)out_h / ch;
+        sc_x = 1.0 / inv_x;
+        sc_y = 1.0 / inv_y;
+        if (sc_x >= 1 && sc_y >= 1) {
+            isx = __double2int_rn(sc_x);
+            isy = __double2int_rn(sc_y);
+            regime = (fabs(sc_x - isx) < DBL_EPSILON && fabs(sc_y - isy) < DBL_EPSILON) ? kInteger : kArea;
         } else {
-            int sx, xa0, xa1, sy, b0, b1;
-            linear_taps(x, cw, inv_x, sc_x, true, sx, xa0, xa1);
-            linear_taps(y, ch, inv_y, sc_y, false, sy, b0, b1);
-            const int sx1 = min(sx + 1, cw - 1);
-            if (sx + 1 >= cw) {
-                xa0 = 2048;
-                xa1 = 0;
-            }
-            const int ry0 = min(sy, ch - 1), ry1 = min(sy + 1, ch - 1);
-            const uint8_t *S0 = roi + (size_t)ry0 * stride, *S1 = roi + (size_t)ry1 * stride;
-#pragma unroll
-            for (int c = 0; c < 3; c++) {
-                const int h0 = S0[3 * sx + c] * xa0 + S0[3 * sx1 + c] * xa1;
-                const int h1 = S1[3 * sx + c] * xa0 + S1[3 * sx1 + c] * xa1;
-                const int v = (((b0 * (h0 >> 4)) >> 16) + ((b1 * (h1 >> 4)) >> 16) + 2) >> 2;
-                val[c] = min(255, max(0, v));
-            }
+            regime = kLinear;
         }
     }
-
-    // ---- normalise (table gather) and store
-    const size_t plane = (size_t)out_h * out_w;
-#pragma unroll
-    for (int c = 0; c < 3; c++) {
-        OutT v;
-        if constexpr (kU8)
-            v = (OutT)val[c];
-        else
-            v = s_lut[val[c] * 3 + c];
-        const size_t o = planar ? ((size_t)i * 3 + c) * plane + pix : ((size_t)i * plane + pix) * 3 + c;
-        out[o] = v;
+    if (regime == kArea || regime == kLinear) {
+        for (int k = threadIdx.x; k < out_w; k += blockDim.x) fill_taps(tx, k, k, regime, cw, inv_x, sc_x, true);
+        for (int k = threadIdx.x; k < out_h; k += blockDim.x) fill_taps(ty, k, k, regime, ch, inv_y, sc_y, false);
     }
+    __syncthreads();
+
+    const uint8_t *roi = base + (ptrdiff_t)(ci - row0) * stride + cj * 3;
+    const int npix = rows * out_w;
+    for (int pix = threadIdx.x; pix < npix; pix += blockDim.x) {
+        const int r = pix / out_w, ox = pix - r * out_w, oy = band0 + r;
+        // ---- trace the output pixel back through the augmentations
+        int y = oy, x = ox;
+        bool filled = false;
+        int val[3] = {0, 0, 0};
+        for (int k = ops.n_ops - 1; k >= 0 && !filled; k--) {
+            const int a = prm[4 + 2 * k], b = prm[5 + 2 * k];
+            const int type = ops.type[k], arg = ops.arg[k];
+            if (type == kOpCutout) {
+                filled = y >= a && y < a + arg && x >= b && x < b + arg;
+            } else if (type == kOpTranslate) {
+                y += a - arg;
+                x += b - arg;
+                filled = y < 0 || y >= out_h || x < 0 || x >= out_w;
+            } else if (type == kOpFlip) {
+                if (a) x = out_w - 1 - x;
+            }
+            if (filled) {
+                val[0] = ops.fill[k][0];
+                val[1] = ops.fill[k][1];
+                val[2] = ops.fill[k][2];
+            }
+        }
+        if (!filled && ok) {
+            if (regime == kCopy) {
+                const uint8_t *p = roi + (size_t)y * stride + x * 3;
+                val[0] = p[0];
+                val[1] = p[1];
+                val[2] = p[2];
+            } else if (regime == kInteger) {
+                int s0 = 0, s1 = 0, s2 = 0;
+                for (int j = 0; j < isy; j++) {
+                    const uint8_t *p = roi + (size_t)(y * isy + j) * stride + (x * isx) * 3;
+                    for (int k = 0; k < isx; k++, p += 3) {
+                        s0 += p[0];
+                        s1 += p[1];
+                        s2 += p[2];
+                    }
+                }
+                if (isx == 2 && isy == 2) {
+                    val[0] = (s0 + 2) >> 2;
+                    val[1] = (s1 + 2) >> 2;
+                    val[2] = (s2 + 2) >> 2;
+                } else {
+                    const float inv = __fdiv_rn(1.f, (float)(isx * isy));
+                    val[0] = sat_round(__fmul_rn((float)s0, inv));
+                    val[1] = sat_round(__fmul_rn((float)s1, inv));
+                    val[2] = sat_round(__fmul_rn((float)s2, inv));
+                }
+            } else if (regime == kArea) {
+                const int xf = tx.first[x], xc = tx.count[x], xn = xc & 0xffff;
+                const float xwl = tx.wl[x], xwm = tx.wm[x], xwr = tx.wr[x];
+                const bool xl = xc & (1 << 16), xr = xc & (1 << 17);
+                const int yf = ty.first[y], yc = ty.count[y], yn = yc & 0xffff;
+                const float ywl = ty.wl[y], ywm = ty.wm[y], ywr = ty.wr[y];
+                const bool yl = yc & (1 << 16), yr = yc & (1 << 17);
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+                for (int j = 0; j < yn; j++) {
+                    const uint8_t *p = roi + (size_t)(yf + j) * stride + xf * 3;
+                    float r0 = 0.f, r1 = 0.f, r2 = 0.f;
+                    for (int k = 0; k < xn; k++, p += 3) {
+                        const float w = (k == 0 && xl) ? xwl : ((k == xn - 1 && xr) ? xwr : xwm);
+                        r0 = __fadd_rn(r0, __fmul_rn((float)p[0], w));
+                        r1 = __fadd_rn(r1, __fmul_rn((float)p[1], w));
+                        r2 = __fadd_rn(r2, __fmul_rn((float)p[2], w));
+                    }
+                    const float beta = (j == 0 && yl) ? ywl : ((j == yn - 1 && yr) ? ywr : ywm);
+                    if (j == 0) {
+                        a0 = __fmul_rn(beta, r0);
+                        a1 = __fmul_rn(beta, r1);
+                        a2 = __fmul_rn(beta, r2);
+                    } else {
+                        a0 = __fadd_rn(a0, __fmul_rn(beta, r0));
+                        a1 = __fadd_rn(a1, __fmul_rn(beta, r1));
+                        a2 = __fadd_rn(a2, __fmul_rn(beta, r2));
+                    }
+                }
+                val[0] = sat_round(a0);
+                val[1] = sat_round(a1);
+                val[2] = sat_round(a2);
+            } else {
+                const int sx = tx.first[x], xw = tx.count[x], xa0 = xw >> 16, xa1 = xw & 0xffff;
+                const int sy = ty.first[y], yw = ty.count[y], b0 = yw >> 16, b1 = yw & 0xffff;
+                const int sx1 = min(sx + 1, cw - 1);
+                const int ry0 = min(sy, ch - 1), ry1 = min(sy + 1, ch - 1);
+                const uint8_t *S0 = roi + (size_t)ry0 * stride, *S1 = roi + (size_t)ry1 * stride;
+#pragma unroll
+                for (int c = 0; c < 3; c++) {
+                    const int h0 = S0[3 * sx + c] * xa0 + S0[3 * sx1 + c] * xa1;
+                    const int h1 = S1[3 * sx + c] * xa0 + S1[3 * sx1 + c] * xa1;
+                    const int v = (((b0 * (h0 >> 4)) >> 16) + ((b1 * (h1 >> 4)) >> 16) + 2) >> 2;
+                    val[c] = min(255, max(0, v));
+                }
+            }
+        }
+        // ---- normalise (table gather) into the shared output tile, in final memory order
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+            OutT v;
+            if constexpr (kU8)
+                v = (OutT)val[c];
+            else
+                v = s_lut[val[c] * 3 + c];
+            s_out[planar ? c * npix + pix : pix * 3 + c] = v;
+        }
+    }
+    __syncthreads();
+
+    // ---- coalesced copy-out: one contiguous run (NHWC) or one per channel (NCHW), 16-byte vectors
+    const size_t plane = (size_t)out_h * out_w;
+    const int runs = planar ? 3 : 1;
+    const int run_elems = planar ? npix : npix * 3;
+    for (int c = 0; c < runs; c++) {
+        OutT *dst = planar ? out + ((size_t)i * 3 + c) * plane + (size_t)band0 * out_w
+                           : out + ((size_t)i * plane + (size_t)band0 * out_w) * 3;
+        const OutT *srcp = s_out + (size_t)c * run_elems;
+        constexpr int kVec = 16 / sizeof(OutT);
+        const bool aligned = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(srcp)) & 15) == 0;
+        const int nvec = aligned ? run_elems / kVec : 0;
+        for (int k = threadIdx.x; k < nvec; k += blockDim.x)
+            reinterpret_cast<uint4 *>(dst)[k] = reinterpret_cast<const uint4 *>(srcp)[k];
+        for (int k = nvec * kVec + threadIdx.x; k < run_elems; k += blockDim.x) dst[k] = srcp[k];
+    }
+}
+
+template <typename OutT>
+static void launch_typed(const ResizeSource &src, int n, const int32_t *params, int n_params, const OpList &ops,
+                         int resize, int out_h, int out_w, int planar, const void *lut, void *out,
+                         const int32_t *status, cudaStream_t stream) {
+    int band = (2048 + out_w - 1) / out_w;
+    if (band < 1) band = 1;
+    if (band > out_h) band = out_h;
+    auto smem_for = [&](int b) {
+        size_t tile = (((size_t)b * out_w * 3 * sizeof(OutT)) + 15) & ~(size_t)15;
+        size_t lutb = (768 * sizeof(OutT) + 15) & ~(size_t)15;
+        return tile + lutb + sizeof(int) * 5 * ((size_t)out_w + out_h);
+    };
+    while (band > 1 && smem_for(band) > 200 * 1024) band /= 2;
+    const size_t smem = smem_for(band);
+    auto kern = resize_augment_kernel<OutT>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    dim3 grid((out_h + band - 1) / band, n);
+    kern<<<grid, 256, smem, stream>>>(src, params, n_params, ops, resize, out_h, out_w, band, planar,
+                                      (const OutT *)lut, (OutT *)out, status);
 }
 
 void launch_resize_augment(const ResizeSource &src, int n, const int32_t *params, int n_params,
                            const OpList &ops, int resize, int out_h, int out_w, int out_kind,
                            const void *lut, void *out, const int32_t *status, cudaStream_t stream) {
     if (n <= 0) return;
-    dim3 grid((out_h * out_w + 255) / 256, n);
     const int planar = out_kind == kOutF16Nchw || out_kind == kOutF32Nchw;
     if (out_kind == kOutU8)
-        resize_augment_kernel<uint8_t><<<grid, 256, 0, stream>>>(src, params, n_params, ops, resize, out_h,
-                                                                 out_w, 0, nullptr, (uint8_t *)out, status);
+        launch_typed<uint8_t>(src, n, params, n_params, ops, resize, out_h, out_w, 0, nullptr, out, status, stream);
     else if (out_kind == kOutF16Nhwc || out_kind == kOutF16Nchw)
-        resize_augment_kernel<uint16_t><<<grid, 256, 0, stream>>>(src, params, n_params, ops, resize, out_h,
-                                                                  out_w, planar, (const uint16_t *)lut,
-                                                                  (uint16_t *)out, status);
+        launch_typed<uint16_t>(src, n, params, n_params, ops, resize, out_h, out_w, planar, lut, out, status, stream);
     else
-        resize_augment_kernel<uint32_t><<<grid, 256, 0, stream>>>(src, params, n_params, ops, resize, out_h,
-                                                                  out_w, planar, (const uint32_t *)lut,
-                                                                  (uint32_t *)out, status);
+        launch_typed<uint32_t>(src, n, params, n_params, ops, resize, out_h, out_w, planar, lut, out, status, stream);
 }
 
 } // namespace ffcvb
