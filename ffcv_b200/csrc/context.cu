@@ -219,14 +219,13 @@ OpList make_oplist(const ffcvb_plan &p) {
     return o;
 }
 
-int pick_subseq_bits(size_t total_scan_bytes, int n_par) {
-    // Aim for about one pass of 1024 threads per image; keep subsequences long enough that the
-    // decoder usually re-synchronises inside one of them.
-    if (n_par <= 0) return 512;
-    size_t bits = total_scan_bytes * 8 / (size_t)n_par;
-    size_t s = align_up(bits / 1024 + 1, 32);
-    if (s < 128) s = 128;
-    if (s > 1024) s = 1024;
+int pick_subseq_bits(size_t max_scan_bytes) {
+    // One pass of the 512 decoder threads should cover the largest image of the batch; the
+    // decoder needs about 7 kbit to re-synchronise, so shorter subsequences only add repair
+    // rounds and longer ones leave threads idle.
+    size_t s = align_up(max_scan_bytes * 8 / 512 + 1, 32);
+    if (s < 512) s = 512;
+    if (s > 2048) s = 2048;
     return (int)s;
 }
 
@@ -345,7 +344,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     std::vector<const RawHuff *> huff_src;
     std::vector<const uint16_t *> mult_src;
     std::vector<int32_t> jpeg_list, par_list, seq_list;
-    size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes_par = 0;
+    size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes_par = 0;  // scan_bytes_par: largest scan
     uint32_t total_blocks = 0;
     int max_pixels = 0;
     for (int i = 0; i < n; i++) {
@@ -384,7 +383,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         d.block_base = total_blocks;
         total_blocks += d.nblocks;
         d.clean_off = clean_bytes;
-        clean_bytes += align_up((size_t)d.scan_len + 32, 16);
+        clean_bytes += align_up((size_t)d.scan_len + 48, 16);
         for (int c = 0; c < h.ncomp; c++) {
             d.plane_off[c] = plane_bytes;
             const size_t pw = (size_t)d.mcus_x * (c == 0 ? d.hs : 1) * 8;
@@ -398,7 +397,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
             seq_list.push_back(i);
         } else {
             par_list.push_back(i);
-            scan_bytes_par += d.scan_len;
+            if (d.scan_len > scan_bytes_par) scan_bytes_par = d.scan_len;
         }
     }
 
@@ -468,7 +467,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.clean_bytes = clean_bytes;
     s.plane_bytes = plane_bytes;
     s.rgb_bytes = rgb_bytes;
-    s.subseq_bits = pick_subseq_bits(scan_bytes_par, s.n_par);
+    s.subseq_bits = pick_subseq_bits(scan_bytes_par);
     s.scan_bytes = s.raw_bytes = s.jpeg_bytes = 0;
     for (int i = 0; i < n; i++) {
         if (descs[i].mode == FFCVB_MODE_JPG) {

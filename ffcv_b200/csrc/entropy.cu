@@ -15,7 +15,7 @@
 
 namespace ffcvb {
 
-constexpr int kEntropyThreads = 1024;
+constexpr int kEntropyThreads = 512;
 
 __device__ __constant__ uint8_t kZigzagNatural[64] = {
     0,  1,  8,  16, 9,  2,  3,  10, 17, 24, 32, 25, 18, 11, 4,  5,  12, 19, 26, 33, 40, 48,
@@ -104,6 +104,31 @@ __device__ __forceinline__ Cursor unpack(uint64_t v) {
     return s;
 }
 
+// Register window over the big-endian bit stream: `buf` holds the next `avail` bits left-aligned.
+struct BitWindow {
+    unsigned long long buf;
+    int avail;
+    uint32_t next; // index of the next 32-bit word to load
+    __device__ __forceinline__ void open(const uint32_t *__restrict__ words, uint32_t p) {
+        const uint32_t i = p >> 5, o = p & 31;
+        const unsigned long long w0 = __byte_perm(words[i], 0, 0x0123);
+        const unsigned long long w1 = __byte_perm(words[i + 1], 0, 0x0123);
+        buf = ((w0 << 32) | w1) << o;
+        avail = 64 - (int)o;
+        next = i + 2;
+    }
+    __device__ __forceinline__ uint32_t top() const { return (uint32_t)(buf >> 32); }
+    __device__ __forceinline__ void consume(const uint32_t *__restrict__ words, int n) {
+        buf <<= n;
+        avail -= n;
+        if (avail <= 32) {
+            const unsigned long long w = __byte_perm(words[next++], 0, 0x0123);
+            buf |= w << (32 - avail);
+            avail += 32;
+        }
+    }
+};
+
 // Decodes symbols from `cur` until its position reaches `end`.  Returns the number of blocks
 // completed.  With WRITE, coefficients go to cf (image base) starting at block `blk`.
 template <bool WRITE>
@@ -115,40 +140,36 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, C
     int done = 0;
     uint32_t p = cur.p;
     int c = cur.c, z = cur.z;
+    if (p >= end) return 0;
+    BitWindow win;
+    win.open(words, p);
+    const HuffTable *tabs = s_tab + ((ncomp == 1 || c < luma) ? 0 : c - luma + 1) * 2;
+    int16_t *out = cf + (size_t)blk * 64;
     while (p < end) {
-        const int comp = (ncomp == 1 || c < luma) ? 0 : c - luma + 1;
-        const HuffTable &t = s_tab[comp * 2 + (z ? 1 : 0)];
-        const uint32_t w = peek32(words, p);
+        const uint32_t w = win.top();
         int len, sym;
-        huff_lookup(t, w, len, sym);
-        int s;
+        huff_lookup(tabs[z ? 1 : 0], w, len, sym);
+        const int s = sym & 15;
         if (z == 0) {
-            s = sym & 15;
-            if (WRITE && blk < nblocks) {
-                int v = s ? extend((w << len) >> (32 - s), s) : 0;
-                cf[(size_t)blk * 64] = (int16_t)v;
-            }
+            if (WRITE && blk < nblocks) out[0] = (int16_t)(s ? extend((w << len) >> (32 - s), s) : 0);
             z = 1;
+        } else if (s == 0) {
+            z = ((sym >> 4) == 15) ? z + 16 : 64;
         } else {
-            s = sym & 15;
-            const int r = sym >> 4;
-            if (s == 0) {
-                z = (r == 15) ? z + 16 : 64;
-            } else {
-                z += r;
-                if (WRITE && z < 64 && blk < nblocks) {
-                    int v = extend((w << len) >> (32 - s), s);
-                    cf[(size_t)blk * 64 + s_zz[z]] = (int16_t)v;
-                }
-                z++;
-            }
+            z += sym >> 4;
+            if (WRITE && z < 64 && blk < nblocks) out[s_zz[z]] = (int16_t)extend((w << len) >> (32 - s), s);
+            z++;
         }
-        p += len + s;
+        const int n = len + s;
+        p += n;
+        win.consume(words, n);
         if (z >= 64) {
             z = 0;
             done++;
             blk++;
+            out += 64;
             c = (c + 1 == bpm) ? 0 : c + 1;
+            tabs = s_tab + ((ncomp == 1 || c < luma) ? 0 : c - luma + 1) * 2;
         }
     }
     cur.p = p;
@@ -211,7 +232,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
             if (keep & (1u << i)) *o++ = b[i];
         clean_len += total;
     }
-    if (tid < 16) cl[clean_len + tid] = 0;
+    if (tid < 32) cl[clean_len + tid] = 0;
     __syncthreads();
 
     const uint32_t *words = reinterpret_cast<const uint32_t *>(cl);
@@ -226,7 +247,12 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
     for (;;) {
         const uint32_t carry_p = (uint32_t)(carry >> 32);
         if (carry_p >= total_bits || blk_base >= d.nblocks) break;
-        const uint32_t g = carry_p / S + tid;
+        const uint32_t first_sub = carry_p / S;
+        // subsequences of this chunk that hold data; threads beyond them stay out of the repair
+        const uint32_t left = (total_bits - first_sub * S + S - 1) / S;
+        const int nsub = left < (uint32_t)kEntropyThreads ? (int)left : kEntropyThreads;
+        const bool active = tid < nsub;
+        const uint32_t g = first_sub + tid;
         const uint32_t sub_start = g * S;
         uint32_t sub_end = sub_start + S;
         if (sub_end > total_bits) sub_end = total_bits;
@@ -235,11 +261,11 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         unsigned long long last_in = ~0ull;
         int my_blocks = 0;
         __syncthreads();
-        for (int iter = 0; iter <= kEntropyThreads; iter++) {
+        for (int iter = 0; iter <= nsub; iter++) {
             const unsigned long long in = s_state[tid];
             __syncthreads();
             int changed = 0;
-            if (in != last_in) {
+            if (active && in != last_in) {
                 Cursor cur = unpack(in);
                 my_blocks = decode_span<false>(words, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz,
                                                nullptr, 0, 0);
@@ -251,12 +277,12 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         }
         int chunk_blocks;
         const int first = block_scan_exclusive(my_blocks, s_warp, chunk_blocks);
-        {
+        if (active) {
             Cursor cur = unpack(s_state[tid]);
             decode_span<true>(words, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
                               blk_base + (uint32_t)first, d.nblocks);
         }
-        carry = s_state[kEntropyThreads];
+        carry = s_state[nsub];
         blk_base += (uint32_t)chunk_blocks;
         __syncthreads();
     }

@@ -110,7 +110,7 @@ class FusedImageExecutor:
                                        self.table_dev.data_ptr() if self.table_dev is not None else 0)
         self.n_params = 4 + 2 * len(ops)
         self.last_params = None
-        self.param_log = None     # set to a list to record (batch indices, parameter table) per batch
+        self.param_log = None     # set to a list to record (epoch, batch, indices, parameter table) per batch
         self.h2d_bytes = 0
         self.launches = 0
 
@@ -138,7 +138,7 @@ class FusedImageExecutor:
         md, heights, widths, params = self.sample_params(batch_indices, epoch, batch_ix)
         self.last_params = params
         if self.param_log is not None:
-            self.param_log.append((np.array(batch_indices), params.copy()))
+            self.param_log.append((epoch, batch_ix, np.array(batch_indices), params.copy()))
         n = len(batch_indices)
         self.ctx.stage(slot, self.file_base_fn(), md['data_ptr'], self.sample_sizes[batch_indices],
                        md['mode'], heights, widths, self.native_plan, params)

@@ -56,13 +56,14 @@ def compare_epoch(loader, field_pos=0, field='image', max_batches=None, tol_lsb=
     import torch as ch
     exe = image_executor(loader, field)
     exe.param_log = []
+    epoch = loader.next_epoch
     outs = []
     for b, batch in enumerate(loader):
         outs.append(batch[field_pos].detach().clone())
         if max_batches is not None and b + 1 >= max_batches:
             break
     ch.cuda.synchronize()
-    log = exe.param_log
+    log = {b: (ix, prm) for (e, b, ix, prm) in exe.param_log if e == epoch}
     exe.param_log = None
     total = 0
     for b, got_t in enumerate(outs):
