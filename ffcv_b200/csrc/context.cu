@@ -1,6 +1,7 @@
 // Host side of libffcv_b200.so: contexts, batch slots, the staging thread pool and the C ABI
 // declared in include/ffcv_b200.h.
 #include <cuda_runtime.h>
+#include <emmintrin.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -12,7 +13,7 @@
 #include <mutex>
 #include <string>
 #include <thread>
-#include <unordered_map>
+#include <chrono>
 #include <vector>
 
 #include "../../include/ffcv_b200.h"
@@ -98,6 +99,29 @@ class Pool {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Copy into the pinned staging buffer with non-temporal stores: the destination is read next by
+// the DMA engine, not by the CPU, so it should not displace the cache or cost a read-for-ownership.
+// dst is 16-byte aligned (payload offsets are).
+void stream_copy(uint8_t *dst, const uint8_t *src, size_t n) {
+    if ((reinterpret_cast<uintptr_t>(dst) & 15) != 0 || n < 4096) {
+        memcpy(dst, src, n);
+        return;
+    }
+    size_t k = 0;
+    for (; k + 64 <= n; k += 64) {
+        __m128i a = _mm_loadu_si128(reinterpret_cast<const __m128i *>(src + k));
+        __m128i b = _mm_loadu_si128(reinterpret_cast<const __m128i *>(src + k + 16));
+        __m128i c = _mm_loadu_si128(reinterpret_cast<const __m128i *>(src + k + 32));
+        __m128i d = _mm_loadu_si128(reinterpret_cast<const __m128i *>(src + k + 48));
+        _mm_stream_si128(reinterpret_cast<__m128i *>(dst + k), a);
+        _mm_stream_si128(reinterpret_cast<__m128i *>(dst + k + 16), b);
+        _mm_stream_si128(reinterpret_cast<__m128i *>(dst + k + 32), c);
+        _mm_stream_si128(reinterpret_cast<__m128i *>(dst + k + 48), d);
+    }
+    if (k < n) memcpy(dst + k, src + k, n - k);
+    _mm_sfence();
+}
+
 struct DevBuf {
     void *p = nullptr;
     size_t cap = 0;
@@ -114,6 +138,7 @@ struct Slot {
     uint32_t total_blocks = 0;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes = 0, raw_bytes = 0, jpeg_bytes = 0;
     bool staged = false;
+    double stage_ms[4] = {0, 0, 0, 0}; // header parse, layout, payload copy, total
     std::vector<JpegHeader> headers;
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool timed = false; // events of the last run are valid
@@ -187,14 +212,6 @@ int grow_host(ffcvb_ctx *ctx, uint8_t *&p, size_t &cap_io, size_t need) {
     cap_io = cap;
     return 0;
 }
-
-struct TableKey {
-    std::string bytes;
-    bool operator==(const TableKey &o) const { return bytes == o.bytes; }
-};
-struct TableKeyHash {
-    size_t operator()(const TableKey &k) const { return std::hash<std::string>()(k.bytes); }
-};
 
 bool valid_plan(const ffcvb_plan *p) {
     if (!p || p->out_h <= 0 || p->out_w <= 0 || p->n_ops < 0 || p->n_ops > FFCVB_MAX_OPS) return false;
@@ -290,6 +307,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.plan = *plan;
     s.n = n;
     const int n_params = 4 + 2 * plan->n_ops;
+    const auto t0 = std::chrono::steady_clock::now();
     std::vector<ImageDesc> descs(n);
     s.headers.resize(n);
 
@@ -320,12 +338,15 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                 d.nblocks = (uint32_t)d.bpm * d.mcus_x * d.mcus_y;
             }
         } else {
-            int r0 = 0, rows = d.height;
+            int r0 = 0, rows = d.height, c0 = 0, cols = d.width;
             if (plan->resize) {
                 const int32_t *p = params + (size_t)i * n_params;
-                if (p[0] >= 0 && p[2] > 0 && p[0] + p[2] <= (int)d.height) {
+                if (p[0] >= 0 && p[2] > 0 && p[0] + p[2] <= (int)d.height && p[1] >= 0 && p[3] > 0 &&
+                    p[1] + p[3] <= (int)d.width) {
                     r0 = p[0];
                     rows = p[2];
+                    c0 = p[1];
+                    cols = p[3];
                 }
             }
             const uint64_t need = (uint64_t)d.height * d.width * 3;
@@ -335,12 +356,14 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
             }
             d.row0 = (uint16_t)r0;
             d.rows = (uint16_t)rows;
-            d.payload_size = (uint32_t)((size_t)rows * d.width * 3);
+            d.col0 = (uint16_t)c0;
+            d.cols = (uint16_t)cols;
+            d.payload_size = (uint32_t)((size_t)rows * cols * 3);
         }
     });
 
+    const auto t1 = std::chrono::steady_clock::now();
     // ---- serial: deduplicate tables, lay the blob out
-    std::unordered_map<TableKey, int, TableKeyHash> huff_ix, mult_ix;
     std::vector<const RawHuff *> huff_src;
     std::vector<const uint16_t *> mult_src;
     std::vector<int32_t> jpeg_list, par_list, seq_list;
@@ -361,22 +384,25 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
             const RawHuff *tabs[2] = {&h.dc[h.td[c]], &h.ac[h.ta[c]]};
             uint8_t *dst[2] = {&d.dc_tab[c], &d.ac_tab[c]};
             for (int k = 0; k < 2; k++) {
-                TableKey key{std::string((const char *)tabs[k]->bits, 17) +
-                             std::string((const char *)tabs[k]->vals, 256)};
-                auto it = huff_ix.find(key);
-                if (it == huff_ix.end()) {
-                    it = huff_ix.emplace(std::move(key), (int)huff_src.size()).first;
+                int found = -1;
+                for (int u = (int)huff_src.size() - 1; u >= 0 && found < 0; u--)
+                    if (huff_src[u] == tabs[k] || (memcmp(huff_src[u]->bits, tabs[k]->bits, 17) == 0 &&
+                                                   memcmp(huff_src[u]->vals, tabs[k]->vals, 256) == 0))
+                        found = u;
+                if (found < 0) {
+                    found = (int)huff_src.size();
                     huff_src.push_back(tabs[k]);
                 }
-                *dst[k] = (uint8_t)it->second;
+                *dst[k] = (uint8_t)found;
             }
-            TableKey qk{std::string((const char *)h.quant[h.tq[c]], 128)};
-            auto qt = mult_ix.find(qk);
-            if (qt == mult_ix.end()) {
-                qt = mult_ix.emplace(std::move(qk), (int)mult_src.size()).first;
+            int qfound = -1;
+            for (int u = (int)mult_src.size() - 1; u >= 0 && qfound < 0; u--)
+                if (memcmp(mult_src[u], h.quant[h.tq[c]], 128) == 0) qfound = u;
+            if (qfound < 0) {
+                qfound = (int)mult_src.size();
                 mult_src.push_back(h.quant[h.tq[c]]);
             }
-            d.q_tab[c] = (uint8_t)qt->second;
+            d.q_tab[c] = (uint8_t)qfound;
         }
         if (huff_src.size() > 255 || mult_src.size() > 255)
             return fail(ctx, FFCVB_E_LIMIT, "more than 255 distinct Huffman or quantisation tables in a batch");
@@ -449,16 +475,31 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     if (!par_list.empty()) memcpy(s.host + s.par_list_off, par_list.data(), 4 * par_list.size());
     if (!seq_list.empty()) memcpy(s.host + s.seq_list_off, seq_list.data(), 4 * seq_list.size());
 
+    const auto t2 = std::chrono::steady_clock::now();
     // ---- parallel: gather the payload bytes into pinned memory
     uint8_t *host = s.host;
     ctx->pool->parallel_for(n, [&](int i) {
         const ImageDesc &d = descs[i];
         if (d.payload_size == 0) return;
         const uint8_t *src = file_base + ptrs[i];
-        if (d.mode == FFCVB_MODE_RAW) src += (size_t)d.row0 * d.width * 3;
-        memcpy(host + d.payload_off, src, d.payload_size);
+        uint8_t *dst = host + d.payload_off;
+        if (d.mode == FFCVB_MODE_RAW && d.cols != d.width) {
+            // only the crop box travels: one run per row
+            const size_t pitch = (size_t)d.width * 3, run = (size_t)d.cols * 3;
+            src += (size_t)d.row0 * pitch + (size_t)d.col0 * 3;
+            for (int r = 0; r < d.rows; r++) memcpy(dst + r * run, src + r * pitch, run);
+        } else {
+            if (d.mode == FFCVB_MODE_RAW) src += (size_t)d.row0 * d.width * 3;
+            stream_copy(dst, src, d.payload_size);
+        }
     });
 
+    const auto t3 = std::chrono::steady_clock::now();
+    auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
+    s.stage_ms[0] = ms(t0, t1);
+    s.stage_ms[1] = ms(t1, t2);
+    s.stage_ms[2] = ms(t2, t3);
+    s.stage_ms[3] = ms(t0, t3);
     s.n_jpeg = (int)jpeg_list.size();
     s.n_par = (int)par_list.size();
     s.n_seq = (int)seq_list.size();
@@ -572,6 +613,12 @@ int ffcvb_rerun_batch(ffcvb_ctx *ctx, int slot, void *stream, void *out_dev) {
 int64_t ffcvb_staged_bytes(const ffcvb_ctx *ctx, int slot) {
     if (!ctx || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return -1;
     return (int64_t)ctx->slots[slot].hdr.total_bytes;
+}
+
+int ffcvb_stage_times(const ffcvb_ctx *ctx, int slot, double *ms) {
+    if (!ctx || !ms || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return FFCVB_E_ARG;
+    for (int k = 0; k < 4; k++) ms[k] = ctx->slots[slot].stage_ms[k];
+    return FFCVB_OK;
 }
 
 int ffcvb_batch_info(const ffcvb_ctx *ctx, int slot, int64_t *info) {

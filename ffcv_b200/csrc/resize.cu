@@ -127,7 +127,7 @@ resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int 
 
     // ---- where the sample's pixels are
     const uint8_t *base;
-    int stride, row0 = 0, img_h, img_w;
+    int stride, row0 = 0, col0 = 0, img_h, img_w;
     bool ok = true;
     if (src.descs) {
         const ImageDesc &d = src.descs[i];
@@ -137,6 +137,8 @@ resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int 
         if (d.mode == 1) {
             base = src.blob + d.payload_off;
             row0 = d.row0;
+            col0 = d.col0;
+            stride = d.cols * 3;
             ok = d.host_status == 0;
         } else {
             base = src.rgb + d.rgb_off;
@@ -181,7 +183,7 @@ resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int 
     }
     __syncthreads();
 
-    const uint8_t *roi = base + (ptrdiff_t)(ci - row0) * stride + cj * 3;
+    const uint8_t *roi = base + (ptrdiff_t)(ci - row0) * stride + (cj - col0) * 3;
     const int npix = rows * out_w;
     for (int pix = threadIdx.x; pix < npix; pix += blockDim.x) {
         const int r = pix / out_w, ox = pix - r * out_w, oy = band0 + r;

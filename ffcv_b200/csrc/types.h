@@ -17,8 +17,8 @@ struct ImageDesc {
     uint16_t mode;         // 0 jpg, 1 raw (ffcv/fields/rgb_image.py:21-23)
     int16_t host_status;   // 0, or a negative code when the host parser rejected the stream
     uint16_t height, width;
-    uint16_t row0;         // raw: first image row present in the staged payload
-    uint16_t rows;         // raw: number of staged rows
+    uint16_t row0, rows;   // raw: first image row present in the staged payload, number of rows
+    uint16_t col0, cols;   // raw: first image column present, number of columns (row pitch = cols * 3)
     // ---- JPEG only ----
     uint32_t scan_off;     // entropy-coded segment, relative to payload_off
     uint32_t scan_len;

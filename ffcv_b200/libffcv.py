@@ -56,6 +56,8 @@ lib.ffcvb_batch_times.argtypes = [c_void_p, c_int, c_void_p]
 lib.ffcvb_batch_times.restype = c_int
 lib.ffcvb_staged_bytes.argtypes = [c_void_p, c_int]
 lib.ffcvb_staged_bytes.restype = c_int64
+lib.ffcvb_stage_times.argtypes = [c_void_p, c_int, c_void_p]
+lib.ffcvb_stage_times.restype = c_int
 lib.ffcvb_batch_info.argtypes = [c_void_p, c_int, c_void_p]
 lib.ffcvb_batch_info.restype = c_int
 lib.ffcvb_batch_launches.argtypes = [c_void_p, c_int]
@@ -139,6 +141,12 @@ class Context:
 
     def staged_bytes(self, slot):
         return int(lib.ffcvb_staged_bytes(self._h, slot))
+
+    def stage_times(self, slot):
+        """Host milliseconds of the slot's last staging: (header parse, layout, payload copy, total)."""
+        ms = np.zeros(4, dtype=np.float64)
+        self._check(lib.ffcvb_stage_times(self._h, slot, ms.ctypes.data), 'ffcvb_stage_times')
+        return ms
 
     def batch_info(self, slot):
         info = np.zeros(8, dtype=np.int64)

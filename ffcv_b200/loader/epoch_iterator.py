@@ -1,12 +1,15 @@
 """Asynchronous batch pump of one epoch (reference: ``ffcv/loader/epoch_iterator.py:33-176``).
 
-Same protocol as the reference: a worker thread walks the batches, each batch uses one slot of a
+Same structure as the reference: a worker thread walks the batches, each batch uses one slot of a
 ring of ``batches_ahead + 2`` buffer sets with its own CUDA stream, results travel through a
 bounded queue, the consumer's stream waits on the slot's stream in ``__next__``, and a slot is
 only refilled after an event recorded on the consumer's stream says the batch that used it
-before has been consumed.  Two differences: what runs on the slot's stream is the native
-decode-and-augment call instead of a host->device copy of decoded pixels, and an exception in
-the worker is handed to the consumer and re-raised there instead of leaving it blocked.
+before has been consumed.  Three differences: what runs on the slot's stream is the native
+decode-and-augment call instead of a host->device copy of decoded pixels; the "consumed" event
+of a batch is recorded when the consumer asks for the next batch (the reference records it at
+hand-over time, which chains every new batch behind the consumer's latest work and keeps copies
+from overlapping compute); and an exception in the worker is handed to the consumer and re-raised
+there instead of leaving it blocked.
 """
 from queue import Full, Queue
 from threading import Event, Thread
@@ -46,16 +49,21 @@ class EpochIterator(Thread):
             self.cuda_streams = [None] * self.slots
         self.buffers = loader.slot_buffers()
         self.slot_done = loader.slot_done_events()
-        self.start_event = None
+        # consumed[s]: recorded on the consumer's stream once the consumer has moved past the batch
+        # that used slot s, i.e. when it asks for the following batch.  The queue bound guarantees
+        # the worker reaches a slot again only after that (it can run batches_ahead + 1 batches
+        # ahead of the batch being consumed and the ring has batches_ahead + 2 slots).  Output
+        # buffers live across epochs, so every slot first waits for what the consumer had queued
+        # when this epoch started.
+        start_event = None
         if self.is_cuda:
-            self.start_event = ch.cuda.Event()
-            self.start_event.record(self.current_stream)
+            start_event = ch.cuda.Event()
+            start_event.record(self.current_stream)
+        self.consumed = [start_event] * self.slots
+        self.last_slot = None
         self.start()
 
     def run(self):
-        # output buffers live across epochs: the first use of every slot waits for whatever the
-        # consumer had queued when this epoch started
-        events = [self.start_event] * self.slots
         slot = 0
         try:
             if self.is_cuda:
@@ -63,7 +71,7 @@ class EpochIterator(Thread):
             for b_ix, ixes in enumerate(self.batches):
                 if self.terminate_event.is_set():
                     return
-                result = self.run_pipeline(b_ix, ixes, slot, events[slot])
+                result = self.run_pipeline(b_ix, ixes, slot, self.consumed[slot])
                 item = (slot, result)
                 while True:
                     try:
@@ -73,14 +81,6 @@ class EpochIterator(Thread):
                         pass
                     if self.terminate_event.is_set():
                         return
-                if self.is_cuda:
-                    # The consumer has been handed batch b_ix - batches_ahead at least, so all the
-                    # work it queued for the slot used batches_ahead + 1 batches ago is on its
-                    # stream: fence that slot's reuse on it.
-                    done_slot = (slot - self.loader.batches_ahead - 1) % self.slots
-                    event = ch.cuda.Event()
-                    event.record(self.current_stream)
-                    events[done_slot] = event
                 slot = (slot + 1) % self.slots
             self.output_queue.put(None)
         except BaseException as exc:  # noqa: BLE001 - forwarded to the consumer
@@ -108,6 +108,11 @@ class EpochIterator(Thread):
             return result
 
     def __next__(self):
+        if self.is_cuda and self.last_slot is not None:
+            event = ch.cuda.Event()
+            event.record(self.current_stream)
+            self.consumed[self.last_slot] = event
+            self.last_slot = None
         item = self.output_queue.get()
         if item is None:
             self.close()
@@ -118,6 +123,7 @@ class EpochIterator(Thread):
         slot, result = item
         if self.is_cuda:
             self.current_stream.wait_stream(self.cuda_streams[slot])
+            self.last_slot = slot
         return result
 
     def __iter__(self):

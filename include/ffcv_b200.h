@@ -125,6 +125,9 @@ int ffcvb_batch_times(ffcvb_ctx *ctx, int slot, float *ms);
 /* Bytes the last staged batch of `slot` moves host->device, and how many of this library's
  * kernels ffcvb_submit_batch launches for it. */
 int64_t ffcvb_staged_bytes(const ffcvb_ctx *ctx, int slot);
+/* Host milliseconds the last ffcvb_stage_batch on `slot` spent in: ms[0] JPEG header parsing,
+ * ms[1] table deduplication and layout, ms[2] payload copy into pinned memory, ms[3] total. */
+int ffcvb_stage_times(const ffcvb_ctx *ctx, int slot, double *ms);
 /* Sizes of the slot's staged batch, for bandwidth accounting: info[0] samples, [1] JPEG samples,
  * [2] 8x8 blocks, [3] entropy-coded bytes, [4] component-plane bytes, [5] decoded RGB bytes,
  * [6] staged raw-pixel bytes, [7] staged JPEG bytes. */
