@@ -68,6 +68,21 @@ lib.ffcvb_transform_device.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_in
                                        POINTER(Plan), c_void_p, c_void_p]
 lib.ffcvb_transform_device.restype = c_int
 
+lib.ffcvb_imdecode_static.argtypes = [c_void_p, c_uint64, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p]
+lib.ffcvb_imdecode_static.restype = c_int
+STATIC_MAX_STREAM_BYTES = 1 << 20
+STATIC_MAX_PADDED_PIXELS = 640 * 640
+
+
+def imdecode_static(jpeg_host: np.ndarray, jpeg_dev_ptr: int, height: int, width: int, rgb_dev_ptr: int,
+                    stream: int = 0):
+    """Decode one JPEG without any allocation by the library: ``jpeg_host`` is the stream in host
+    memory, ``jpeg_dev_ptr`` the address of the same bytes on the GPU, ``rgb_dev_ptr`` the address of
+    a ``height * width * 3`` byte output buffer on the GPU.  Asynchronous on ``stream``.  Returns the
+    library's status code (0 on success, -6 when the image exceeds the fixed scratch)."""
+    return lib.ffcvb_imdecode_static(jpeg_host.ctypes.data, jpeg_host.size, jpeg_dev_ptr, height, width,
+                                     rgb_dev_ptr, stream or None)
+
 
 def make_plan(out_h, out_w, resize, out_kind, ops=(), lut_dev=0):
     """ops: sequence of (type, arg, fill) with fill a 3-sequence of ints."""

@@ -145,6 +145,31 @@ int ffcvb_batch_status(ffcvb_ctx *ctx, int slot, void *stream, int32_t *status, 
 int ffcvb_transform_device(ffcvb_ctx *ctx, void *stream, const uint8_t *src_dev, int n, int h,
                            int w, const ffcvb_plan *plan, const int32_t *params, void *out_dev);
 
+/* ---- decode without allocating -----------------------------------------------------------
+ * No counterpart in the reference.  For callers that must not allocate GPU memory while they
+ * run: a process that handed all device memory to its own pool at start-up, a plugin living
+ * inside another framework's allocator, a latency-critical loop that cannot afford the
+ * device-wide synchronisation a cudaMalloc / cudaFree may cause.  Decodes ONE baseline JPEG
+ * (same streams and same pixels as `imdecode`) into packed RGB, height * width * 3 bytes.
+ *   jpeg_host : the stream in host memory (only its headers are read, on the host)
+ *   jpeg_dev  : the same `jpeg_size` bytes already in DEVICE memory (the caller copied them)
+ *   rgb_dev   : DEVICE output buffer of the caller
+ * The work is queued on `stream` and the call returns; a corrupt entropy segment is not reported.
+ * All scratch (unstuffed bit stream, coefficients, component planes, tables) lives in a fixed
+ * array inside the library image, about 4.7 MB that every GPU loading the library holds until
+ * exit, which bounds one call to FFCVB_STATIC_MAX_STREAM_BYTES of JPEG data and
+ * FFCVB_STATIC_MAX_PADDED_PIXELS luma samples after padding both sides up to whole MCUs (multiples
+ * of 8 or 16); larger inputs are refused with FFCVB_E_LIMIT and a message on stderr.  The call
+ * itself makes no cudaMalloc, cudaFree or other allocating call.  The first call on a device
+ * looks up the array's device address (cudaGetSymbolAddress); make that first call outside any
+ * stream capture.  All calls share the one array, which keeps what the previous call left
+ * (the parts that must start at zero are cleared on the stream each time): two calls whose GPU
+ * work can overlap -- different streams, or different threads without ordering -- race on it. */
+#define FFCVB_STATIC_MAX_STREAM_BYTES (1u << 20)
+#define FFCVB_STATIC_MAX_PADDED_PIXELS (640u * 640u)
+int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_size, const uint8_t *jpeg_dev,
+                          uint32_t height, uint32_t width, uint8_t *rgb_dev, void *stream);
+
 /* ---- single-image entry points with the reference's exact signatures --------------------
  * Drop-in for the symbols ffcv/libffcv.py:22-55 binds with ctypes.  HOST pointers in and out;
  * each call copies to the GPU, runs the kernels and copies back, synchronously, on a process-wide
