@@ -138,9 +138,14 @@ struct Slot {
     uint32_t total_blocks = 0;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes = 0, raw_bytes = 0, jpeg_bytes = 0;
     bool staged = false;
+    bool direct = false; // payloads are gathered by the GPU from pinned host memory
     double stage_ms[4] = {0, 0, 0, 0}; // header parse, layout, payload copy, total
     std::vector<JpegHeader> headers;
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    // payload gather runs on its own high-priority stream so that its few CTAs are placed ahead of
+    // the large grids other slots have queued, and the PCIe transfer overlaps their compute
+    cudaStream_t gather_stream = nullptr;
+    cudaEvent_t ev_begin = nullptr, ev_gathered = nullptr;
     bool timed = false; // events of the last run are valid
 };
 
@@ -279,6 +284,9 @@ void ffcvb_destroy(ffcvb_ctx *ctx) {
             if (b->p) cudaFree(b->p);
         for (auto &e : s.ev)
             if (e) cudaEventDestroy(e);
+        if (s.gather_stream) cudaStreamDestroy(s.gather_stream);
+        if (s.ev_begin) cudaEventDestroy(s.ev_begin);
+        if (s.ev_gathered) cudaEventDestroy(s.ev_gathered);
     }
     for (auto &a : ctx->aux) {
         if (a.dev.p) cudaFree(a.dev.p);
@@ -308,6 +316,20 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.n = n;
     const int n_params = 4 + 2 * plan->n_ops;
     const auto t0 = std::chrono::steady_clock::now();
+    // A source that lives in pinned (page-locked, device-mapped) host memory is not copied by the
+    // CPU: the GPU gathers the payloads itself.
+    uint64_t src_dev_base = 0;
+    {
+        cudaPointerAttributes attr;
+        memset(&attr, 0, sizeof(attr));
+        if (cudaPointerGetAttributes(&attr, file_base) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+            attr.devicePointer != nullptr)
+            src_dev_base = (uint64_t)(uintptr_t)attr.devicePointer;
+        else
+            cudaGetLastError(); // pageable memory: not an error
+    }
+    const bool direct = src_dev_base != 0;
+    s.direct = direct;
     std::vector<ImageDesc> descs(n);
     s.headers.resize(n);
 
@@ -345,8 +367,10 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                     p[1] + p[3] <= (int)d.width) {
                     r0 = p[0];
                     rows = p[2];
-                    c0 = p[1];
-                    cols = p[3];
+                    if (!direct) { // the CPU copies just the crop box; the GPU gather takes whole rows
+                        c0 = p[1];
+                        cols = p[3];
+                    }
                 }
             }
             const uint64_t need = (uint64_t)d.height * d.width * 3;
@@ -359,7 +383,9 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
             d.col0 = (uint16_t)c0;
             d.cols = (uint16_t)cols;
             d.payload_size = (uint32_t)((size_t)rows * cols * 3);
+            if (direct && rows > 0) d.src_addr = src_dev_base + ptrs[i] + (uint64_t)r0 * d.width * 3;
         }
+        if (direct && modes[i] == FFCVB_MODE_JPG) d.src_addr = src_dev_base + ptrs[i];
     });
 
     const auto t1 = std::chrono::steady_clock::now();
@@ -450,13 +476,14 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     off = align_up(off + sizeof(int32_t) * seq_list.size(), 16);
     hd.payload_off = off;
     for (int i = 0; i < n; i++) {
-        descs[i].payload_off = off;
-        off = align_up(off + descs[i].payload_size, kPayloadAlign);
+        // gathered payloads keep their source alignment mod 16 so both sides move in 16-byte words
+        descs[i].payload_off = off + (direct ? (descs[i].src_addr & 15) : 0);
+        off = align_up(descs[i].payload_off + descs[i].payload_size, kPayloadAlign);
     }
     hd.total_bytes = off;
 
     int rc;
-    if ((rc = grow_host(ctx, s.host, s.host_cap, off + 64))) return rc;
+    if ((rc = grow_host(ctx, s.host, s.host_cap, (direct ? hd.payload_off : off) + 64))) return rc;
     if ((rc = grow_dev(ctx, s.blob, off + 64))) return rc;
     if ((rc = grow_dev(ctx, s.clean, clean_bytes + 64))) return rc;
     if ((rc = grow_dev(ctx, s.coef, (size_t)total_blocks * 128 + 64))) return rc;
@@ -478,7 +505,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     const auto t2 = std::chrono::steady_clock::now();
     // ---- parallel: gather the payload bytes into pinned memory
     uint8_t *host = s.host;
-    ctx->pool->parallel_for(n, [&](int i) {
+    if (!direct) ctx->pool->parallel_for(n, [&](int i) {
         const ImageDesc &d = descs[i];
         if (d.payload_size == 0) return;
         const uint8_t *src = file_base + ptrs[i];
@@ -532,7 +559,23 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
             if (!e) CU(cudaEventCreate(&e));
         CU(cudaEventRecord(s.ev[0], st));
     }
-    if (copy) CU(cudaMemcpyAsync(blob, s.host, hd.total_bytes, cudaMemcpyHostToDevice, st));
+    if (copy && !s.direct) {
+        CU(cudaMemcpyAsync(blob, s.host, hd.total_bytes, cudaMemcpyHostToDevice, st));
+    } else if (copy) {
+        if (!s.gather_stream) {
+            int lo = 0, hi = 0;
+            CU(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+            CU(cudaStreamCreateWithPriority(&s.gather_stream, cudaStreamNonBlocking, hi));
+            CU(cudaEventCreateWithFlags(&s.ev_begin, cudaEventDisableTiming));
+            CU(cudaEventCreateWithFlags(&s.ev_gathered, cudaEventDisableTiming));
+        }
+        CU(cudaEventRecord(s.ev_begin, st)); // everything the caller ordered before this batch
+        CU(cudaStreamWaitEvent(s.gather_stream, s.ev_begin, 0));
+        CU(cudaMemcpyAsync(blob, s.host, hd.payload_off, cudaMemcpyHostToDevice, s.gather_stream));
+        launch_gather_payloads(reinterpret_cast<const ImageDesc *>(blob + hd.desc_off), s.n, blob, s.gather_stream);
+        CU(cudaEventRecord(s.ev_gathered, s.gather_stream));
+        CU(cudaStreamWaitEvent(st, s.ev_gathered, 0));
+    }
     if (prof) CU(cudaEventRecord(s.ev[1], st));
     const ImageDesc *descs = reinterpret_cast<const ImageDesc *>(blob + hd.desc_off);
     const HuffTable *huff = reinterpret_cast<const HuffTable *>(blob + hd.huff_off);
@@ -638,7 +681,7 @@ int ffcvb_batch_info(const ffcvb_ctx *ctx, int slot, int64_t *info) {
 int ffcvb_batch_launches(const ffcvb_ctx *ctx, int slot) {
     if (!ctx || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return -1;
     const Slot &s = ctx->slots[slot];
-    int k = 1; // fused resize/augment/normalise
+    int k = 1 + (s.direct ? 1 : 0); // fused resize/augment/normalise (+ payload gather)
     if (s.n_jpeg > 0) k += 2 + (s.n_par > 0) + (s.n_seq > 0);
     return k;
 }

@@ -171,6 +171,45 @@ color_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ li
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Payload gather from pinned host memory, so that the host CPU never touches the sample bytes.
+// 16 CTAs of 256 threads with four 16-byte loads in flight each (256 KB outstanding) already fill
+// the PCIe link (51 GB/s measured); more outstanding system-memory reads only congest the memory
+// system for the decode kernels running beside it (48 x 512 threads halved a concurrent HBM copy).
+__global__ void __launch_bounds__(256)
+gather_payloads_kernel(const ImageDesc *__restrict__ descs, int n, uint8_t *__restrict__ blob) {
+    for (int i = blockIdx.x; i < n; i += gridDim.x) {
+        const ImageDesc &d = descs[i];
+        if (d.src_addr == 0 || d.payload_size == 0) continue;
+        const uint8_t *src = reinterpret_cast<const uint8_t *>(d.src_addr);
+        uint8_t *dst = blob + d.payload_off;
+        const uint32_t size = d.payload_size;
+        uint32_t head = (uint32_t)((16 - (d.src_addr & 15)) & 15);
+        if (head > size) head = size;
+        if ((reinterpret_cast<uintptr_t>(dst) & 15) != (d.src_addr & 15)) head = size; // never: bytes only
+        for (uint32_t k = threadIdx.x; k < head; k += blockDim.x) dst[k] = src[k];
+        const uint32_t nvec = (size - head) >> 4;
+        const uint4 *s16 = reinterpret_cast<const uint4 *>(src + head);
+        uint4 *d16 = reinterpret_cast<uint4 *>(dst + head);
+        uint32_t k = threadIdx.x;
+        for (; k + 3 * blockDim.x < nvec; k += 4 * blockDim.x) {
+            const uint4 a = s16[k], b = s16[k + blockDim.x], c = s16[k + 2 * blockDim.x], e = s16[k + 3 * blockDim.x];
+            d16[k] = a;
+            d16[k + blockDim.x] = b;
+            d16[k + 2 * blockDim.x] = c;
+            d16[k + 3 * blockDim.x] = e;
+        }
+        for (; k < nvec; k += blockDim.x) d16[k] = s16[k];
+        for (uint32_t t = head + (nvec << 4) + threadIdx.x; t < size; t += blockDim.x) dst[t] = src[t];
+    }
+}
+
+void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, cudaStream_t stream) {
+    if (n <= 0) return;
+    const int grid = n < 16 ? n : 16;
+    gather_payloads_kernel<<<grid, 256, 0, stream>>>(descs, n, blob);
+}
+
 void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32_t total_blocks,
                  const MultTable *mult, const int16_t *coef, uint8_t *planes, cudaStream_t stream) {
     if (total_blocks == 0) return;

@@ -33,6 +33,7 @@ struct ImageDesc {
     uint64_t clean_off;    // byte offset of the unstuffed scan in the bitstream scratch (4-aligned)
     uint64_t plane_off[kMaxComponents]; // byte offsets of the Y/Cb/Cr planes in the plane scratch
     uint64_t rgb_off;      // byte offset of the decoded h*w*3 image in the RGB scratch
+    uint64_t src_addr;     // device-visible address of the payload in pinned host memory (0: staged copy)
 };
 
 // Canonical Huffman code (ITU-T T.81 Annex C) prepared for table-driven decoding.

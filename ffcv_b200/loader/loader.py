@@ -70,6 +70,12 @@ class Loader:
         Batches prepared in advance.
     recompile : bool
         Rebuild the pipeline executables every epoch.
+    pin_file : bool
+        (not in the reference) Keep the whole file in page-locked host memory and let the GPU
+        fetch each batch's bytes itself over PCIe instead of staging them with CPU threads: no
+        host core touches sample bytes, at the price of some GPU throughput (the gather shares
+        the memory system with the decode kernels) and of one pinned copy of the file per
+        process.  Default off; ``FFCV_B200_PIN_FILE=1`` turns it on.
     """
 
     def __init__(self, fname: str, batch_size: int, num_workers: int = -1,
@@ -78,7 +84,8 @@ class Loader:
                  distributed: bool = False, seed: int = None, indices: Sequence[int] = None,
                  pipelines: Mapping[str, Sequence[Union[Operation, ch.nn.Module]]] = {},
                  custom_fields: Mapping[str, Type[Field]] = {}, drop_last: bool = True,
-                 batches_ahead: int = 3, recompile: bool = False, order_kwargs: dict = dict()):
+                 batches_ahead: int = 3, recompile: bool = False, order_kwargs: dict = dict(),
+                 pin_file: bool = None):
         if distributed and order == OrderOption.RANDOM and (seed is None):
             print('Warning: no ordering seed was specified with distributed=True. '
                   'Setting seed to 0 to match PyTorch distributed sampler.')
@@ -90,7 +97,7 @@ class Loader:
             'fname': fname, 'batch_size': batch_size, 'num_workers': num_workers, 'os_cache': os_cache,
             'order': order, 'distributed': distributed, 'seed': seed, 'indices': indices,
             'pipelines': pipelines, 'drop_last': drop_last, 'batches_ahead': batches_ahead,
-            'recompile': recompile,
+            'recompile': recompile, 'pin_file': pin_file,
         }
         self.fname = fname
         self.batch_size = batch_size
@@ -109,7 +116,10 @@ class Loader:
         else:
             self.indices = np.array(indices)
 
-        self.memory_manager: MemoryManager = OSCacheManager(self.reader)
+        if pin_file is None:
+            pin_file = environ.get('FFCV_B200_PIN_FILE', '0') == '1'
+        self.pin_file = bool(pin_file)
+        self.memory_manager: MemoryManager = OSCacheManager(self.reader, pin=self.pin_file)
 
         if order in ORDER_MAP:
             self.traversal_order: TraversalOrder = ORDER_MAP[order](self)

@@ -50,15 +50,48 @@ class MemoryManager:
 
 
 class OSCacheManager(MemoryManager):
-    def __init__(self, reader):
+    """``pin=False``: the file is memory-mapped (page cache) and the native staging threads copy
+    each batch's bytes into pinned buffers.  ``pin=True``: the whole file is read once into
+    page-locked host memory; the native library notices that its source is pinned and lets the GPU
+    gather every batch's payloads over PCIe itself, so no CPU core touches sample bytes."""
+
+    def __init__(self, reader, pin=False):
         super().__init__(reader)
         self.mmap = None
+        self.pin = bool(pin)
+        self.pinned = False
+        self._keepalive = None
         self.context = MemoryContext(self)
 
     def open(self):
         if self.mmap is None:
-            self.mmap = np.memmap(self.reader.file_name, 'uint8', mode='r')
+            if self.pin:
+                try:
+                    self.mmap = self._read_pinned()
+                    self.pinned = True
+                except Exception as exc:  # not enough lockable memory, no CUDA: keep the staged path
+                    print(f'ffcv_b200: could not pin {self.reader.file_name} ({exc}); using the page cache')
+                    self.pin = False
+            if self.mmap is None:
+                self.mmap = np.memmap(self.reader.file_name, 'uint8', mode='r')
         return self.mmap
+
+    def _read_pinned(self):
+        import os
+        import torch as ch
+        size = os.path.getsize(self.reader.file_name)
+        buf = ch.empty(size, dtype=ch.uint8, pin_memory=True)
+        view = buf.numpy()
+        with open(self.reader.file_name, 'rb', buffering=0) as fp:
+            done = 0
+            mv = memoryview(view)
+            while done < size:
+                got = fp.readinto(mv[done:done + (64 << 20)])
+                if not got:
+                    raise IOError('short read')
+                done += got
+        self._keepalive = buf
+        return view
 
     def file_base(self):
         return self.open().ctypes.data

@@ -119,3 +119,38 @@ def write_dataset(cfg_id, path, count=None, num_workers=-1, page_size=None):
                            num_workers=num_workers, **kwargs)
     writer.from_indexed_dataset(SyntheticImageDataset(cfg_id, count), chunksize=16)
     return path
+
+
+def replicate_samples(path, count):
+    """Rewrites the tables of a freshly written file so that it presents ``count`` samples that
+    cycle through the distinct samples already stored (sample k points at the payload of sample
+    k mod distinct).  Lets a benchmark run epochs of a configuration's real length over a bounded
+    set of distinct images; the payload pages are untouched."""
+    from .reader import Reader
+    from .types import ALLOC_TABLE_TYPE, FieldDescType, HeaderType
+    r = Reader(path)
+    distinct = r.num_samples
+    if count <= distinct:
+        return path
+    reps = -(-count // distinct)
+    metadata = np.tile(r.metadata, reps)[:count]
+    first_payload = int(r.alloc_table['ptr'].min())
+    header_bytes = HeaderType.itemsize + FieldDescType.itemsize * r.num_fields + metadata.nbytes
+    if header_bytes > first_payload:
+        raise ValueError('metadata of the replicated samples does not fit before the first data page')
+    order = np.argsort(r.alloc_table['sample_id'], kind='stable')
+    base = r.alloc_table[order]
+    table = np.tile(base, reps)
+    table['sample_id'] = np.repeat(np.arange(reps, dtype=np.uint64), len(base)) * np.uint64(distinct) + table['sample_id']
+    table = table[table['sample_id'] < count]
+    header = np.array(r.header)
+    header['num_samples'] = count
+    with open(path, 'r+b') as fp:
+        fp.seek(0)
+        fp.write(header.tobytes())
+        fp.seek(HeaderType.itemsize + FieldDescType.itemsize * r.num_fields)
+        fp.write(metadata.tobytes())
+        fp.seek(int(r.header['alloc_table_ptr']))
+        fp.write(table.astype(ALLOC_TABLE_TYPE).tobytes())
+        fp.truncate()
+    return path

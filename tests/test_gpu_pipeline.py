@@ -74,14 +74,18 @@ def test_config1_lowres_jpeg_rrc160(datasets):
     compare_epoch(loader)
 
 
-def test_config2_fullres_mix_rrc224(datasets):
+@pytest.mark.parametrize('pin_file', [False, True], ids=['staged', 'pinned_gather'])
+def test_config2_fullres_mix_rrc224(datasets, pin_file):
+    """Both ways the bytes can reach the GPU: staged by CPU threads from the memory-mapped file
+    (crop box of raw samples only), and gathered by the GPU from a pinned copy of the file."""
     from ffcv_b200 import OrderOption
     from ffcv_b200.fields.decoders import RandomResizedCropRGBImageDecoder
     from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, ToTorchImage
     pipes = {'image': [RandomResizedCropRGBImageDecoder((224, 224)), RandomHorizontalFlip(),
                        NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()],
              'label': None}
-    loader = _loader(datasets[2], 32, pipes, order=OrderOption.QUASI_RANDOM)
+    loader = _loader(datasets[2], 32, pipes, order=OrderOption.QUASI_RANDOM, pin_file=pin_file)
+    assert loader.memory_manager.open() is not None and loader.memory_manager.pinned == pin_file
     modes = loader.reader.metadata['f0']['mode']
     assert 0 < modes.mean() < 1  # both raw and jpg samples present
     compare_epoch(loader)
