@@ -4,6 +4,7 @@
 #include <emmintrin.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
 
@@ -133,7 +134,8 @@ struct Slot {
     DevBuf blob, clean, coef, planes, rgb, status;
     BatchHeader hdr{};
     ffcvb_plan plan{};
-    int n = 0, n_jpeg = 0, n_par = 0, n_seq = 0, max_pixels = 0, subseq_bits = 512;
+    int n = 0, n_jpeg = 0, n_par = 0, n_seq = 0, max_pixels = 0, subseq_bits = 512, entropy_threads = 512;
+    int n_quad = 0, n_other = 0, max_w = 0, max_h = 0;
     uint64_t jpeg_list_off = 0, par_list_off = 0, seq_list_off = 0;
     uint32_t total_blocks = 0;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes = 0, raw_bytes = 0, jpeg_bytes = 0;
@@ -395,7 +397,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     std::vector<int32_t> jpeg_list, par_list, seq_list;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes_par = 0;  // scan_bytes_par: largest scan
     uint32_t total_blocks = 0;
-    int max_pixels = 0;
+    int max_pixels = 0, max_w = 0, max_h = 0, n_quad = 0, n_other = 0;
     for (int i = 0; i < n; i++) {
         ImageDesc &d = descs[i];
         if (d.mode != FFCVB_MODE_JPG) continue;
@@ -445,6 +447,12 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         d.rgb_off = rgb_bytes;
         rgb_bytes += align_up((size_t)d.height * d.width * 3, 16);
         if ((int)d.height * d.width > max_pixels) max_pixels = (int)d.height * d.width;
+        if (d.width > max_w) max_w = d.width;
+        if (d.height > max_h) max_h = d.height;
+        if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3)
+            n_quad++;
+        else
+            n_other++;
         if (d.restart_interval) {
             seq_list.push_back(i);
         } else {
@@ -532,10 +540,19 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.n_seq = (int)seq_list.size();
     s.total_blocks = total_blocks;
     s.max_pixels = max_pixels;
+    s.max_w = max_w;
+    s.max_h = max_h;
+    s.n_quad = n_quad;
+    s.n_other = n_other;
     s.clean_bytes = clean_bytes;
     s.plane_bytes = plane_bytes;
     s.rgb_bytes = rgb_bytes;
     s.subseq_bits = pick_subseq_bits(scan_bytes_par);
+    s.entropy_threads = 512;
+    // tuning overrides
+    if (const char *e = getenv("FFCV_B200_SUBSEQ_BITS")) s.subseq_bits = (atoi(e) + 31) / 32 * 32;
+    if (const char *e = getenv("FFCV_B200_ENTROPY_THREADS")) s.entropy_threads = atoi(e);
+    if (s.subseq_bits < 64) s.subseq_bits = 64;
     s.scan_bytes = s.raw_bytes = s.jpeg_bytes = 0;
     for (int i = 0; i < n; i++) {
         if (descs[i].mode == FFCVB_MODE_JPG) {
@@ -589,12 +606,13 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         const int32_t *sl = reinterpret_cast<const int32_t *>(blob + s.seq_list_off);
         if (s.total_blocks) CU(cudaMemsetAsync(s.coef.p, 0, (size_t)s.total_blocks * 128, st));
         launch_entropy_decode(descs, pl, s.n_par, sl, s.n_seq, blob, huff, (uint8_t *)s.clean.p,
-                              (int16_t *)s.coef.p, status, s.subseq_bits, st);
+                              (int16_t *)s.coef.p, status, s.subseq_bits, s.entropy_threads, st);
         if (prof) CU(cudaEventRecord(s.ev[2], st));
         launch_idct(descs, jl, s.n_jpeg, s.total_blocks, mult, (const int16_t *)s.coef.p,
                     (uint8_t *)s.planes.p, st);
         if (prof) CU(cudaEventRecord(s.ev[3], st));
-        launch_color(descs, jl, s.n_jpeg, s.max_pixels, (const uint8_t *)s.planes.p, (uint8_t *)s.rgb.p, st);
+        launch_color(descs, jl, s.n_jpeg, s.n_quad, s.n_other, s.max_w, s.max_h, (const uint8_t *)s.planes.p,
+                     (uint8_t *)s.rgb.p, s.plan.resize ? params : nullptr, (int)hd.n_params, st);
         if (prof) CU(cudaEventRecord(s.ev[4], st));
     } else if (prof) {
         for (int k = 2; k <= 4; k++) CU(cudaEventRecord(s.ev[k], st));
@@ -682,7 +700,7 @@ int ffcvb_batch_launches(const ffcvb_ctx *ctx, int slot) {
     if (!ctx || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return -1;
     const Slot &s = ctx->slots[slot];
     int k = 1 + (s.direct ? 1 : 0); // fused resize/augment/normalise (+ payload gather)
-    if (s.n_jpeg > 0) k += 2 + (s.n_par > 0) + (s.n_seq > 0);
+    if (s.n_jpeg > 0) k += 1 + (s.n_quad > 0) + (s.n_other > 0) + (s.n_par > 0) + (s.n_seq > 0);
     return k;
 }
 

@@ -15,7 +15,6 @@
 
 namespace ffcvb {
 
-constexpr int kEntropyThreads = 512;
 
 __device__ __constant__ uint8_t kZigzagNatural[64] = {
     0,  1,  8,  16, 9,  2,  3,  10, 17, 24, 32, 25, 18, 11, 4,  5,  12, 19, 26, 33, 40, 48,
@@ -51,35 +50,37 @@ __device__ __forceinline__ int block_scan_exclusive(int v, int *s_warp, int &tot
     return r;
 }
 
-// 32 bits of the big-endian bit stream starting at bit p.
+// 32 bits of the bit stream starting at bit p.  The unstuffed stream is stored as 32-bit words
+// whose most significant bit comes first, so two word loads and one funnel shift do it.
 __device__ __forceinline__ uint32_t peek32(const uint32_t *__restrict__ words, uint32_t p) {
-    uint32_t i = p >> 5;
-    uint32_t w0 = __byte_perm(words[i], 0, 0x0123);
-    uint32_t w1 = __byte_perm(words[i + 1], 0, 0x0123);
-    return __funnelshift_l(w1, w0, p & 31);
+    const uint32_t i = p >> 5;
+    return __funnelshift_l(words[i + 1], words[i], p);
 }
 
-// Length and symbol of the Huffman code at the top of w.  An invalid code consumes 16 bits and
-// yields symbol 0, so that speculative decoding always makes progress.
+// Length and symbol of the Huffman code at the top of w: at most two dependent table reads.  An
+// invalid code consumes 16 bits and yields symbol 0, so that speculative decoding always makes
+// progress.
 __device__ __forceinline__ void huff_lookup(const HuffTable &t, uint32_t w, int &len, int &sym) {
     uint32_t e = t.look[w >> 23];
-    if (e) {
-        len = e >> 8;
-        sym = e & 255;
-        return;
-    }
-    int code = w >> 16;
-    len = 16;
-    sym = 0;
+    if (e & 0x8000u) {
+        if (e != 0xFFFFu) {
+            e = t.sub[e & 0x7fffu][(w >> 16) & 127];
+        } else {
+            // more long-code prefixes than sub-tables (never with the tables encoders emit)
+            const int code = w >> 16;
+            e = 0;
 #pragma unroll 1
-    for (int l = 10; l <= 16; l++) {
-        int c = code >> (16 - l);
-        if (c <= t.maxcode[l]) {
-            len = l;
-            sym = t.vals[(t.valoff[l] + c) & 255];
-            return;
+            for (int l = 10; l <= 16; l++) {
+                const int c = code >> (16 - l);
+                if (c <= t.maxcode[l]) {
+                    e = (uint32_t)(l << 8) | t.vals[(t.valoff[l] + c) & 255];
+                    break;
+                }
+            }
         }
     }
+    len = e ? (int)(e >> 8) : 16;
+    sym = (int)(e & 255);
 }
 
 __device__ __forceinline__ int extend(uint32_t bits, int s) {
@@ -104,33 +105,11 @@ __device__ __forceinline__ Cursor unpack(uint64_t v) {
     return s;
 }
 
-// Register window over the big-endian bit stream: `buf` holds the next `avail` bits left-aligned.
-struct BitWindow {
-    unsigned long long buf;
-    int avail;
-    uint32_t next; // index of the next 32-bit word to load
-    __device__ __forceinline__ void open(const uint32_t *__restrict__ words, uint32_t p) {
-        const uint32_t i = p >> 5, o = p & 31;
-        const unsigned long long w0 = __byte_perm(words[i], 0, 0x0123);
-        const unsigned long long w1 = __byte_perm(words[i + 1], 0, 0x0123);
-        buf = ((w0 << 32) | w1) << o;
-        avail = 64 - (int)o;
-        next = i + 2;
-    }
-    __device__ __forceinline__ uint32_t top() const { return (uint32_t)(buf >> 32); }
-    __device__ __forceinline__ void consume(const uint32_t *__restrict__ words, int n) {
-        buf <<= n;
-        avail -= n;
-        if (avail <= 32) {
-            const unsigned long long w = __byte_perm(words[next++], 0, 0x0123);
-            buf |= w << (32 - avail);
-            avail += 32;
-        }
-    }
-};
-
 // Decodes symbols from `cur` until its position reaches `end`.  Returns the number of blocks
 // completed.  With WRITE, coefficients go to cf (image base) starting at block `blk`.
+// The 32 lanes of a warp walk unrelated parts of the stream, so the step is written as straight
+// line code with selects (DC / AC / end-of-block / zero-run / block end all take the same path);
+// codes longer than the 9-bit first-level table cost one more table read.
 template <bool WRITE>
 __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, Cursor &cur,
                                            uint32_t end, int bpm, int luma, int ncomp,
@@ -140,37 +119,33 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, C
     int done = 0;
     uint32_t p = cur.p;
     int c = cur.c, z = cur.z;
-    if (p >= end) return 0;
-    BitWindow win;
-    win.open(words, p);
-    const HuffTable *tabs = s_tab + ((ncomp == 1 || c < luma) ? 0 : c - luma + 1) * 2;
+    int comp2 = (ncomp == 1 || c < luma) ? 0 : 2 * (c - luma + 1);
     int16_t *out = cf + (size_t)blk * 64;
     while (p < end) {
-        const uint32_t w = win.top();
+        const uint32_t w = peek32(words, p);
+        const bool dc = z == 0;
+        const HuffTable &t = s_tab[comp2 + (dc ? 0 : 1)];
         int len, sym;
-        huff_lookup(tabs[z ? 1 : 0], w, len, sym);
-        const int s = sym & 15;
-        if (z == 0) {
-            if (WRITE && blk < nblocks) out[0] = (int16_t)(s ? extend((w << len) >> (32 - s), s) : 0);
-            z = 1;
-        } else if (s == 0) {
-            z = ((sym >> 4) == 15) ? z + 16 : 64;
-        } else {
-            z += sym >> 4;
-            if (WRITE && z < 64 && blk < nblocks) out[s_zz[z]] = (int16_t)extend((w << len) >> (32 - s), s);
-            z++;
+        huff_lookup(t, w, len, sym);
+        const int s = sym & 15, r = sym >> 4;
+        const int zpos = dc ? 0 : z + r; // where this symbol's coefficient goes, if it has one
+        if (WRITE) {
+            if (s != 0 && zpos < 64 && blk < nblocks)
+                out[dc ? 0 : s_zz[zpos]] = (int16_t)extend((w << len) >> (32 - s), s);
         }
+        // AC without magnitude bits: end of block, or (r == 15) a run of 16 zeros
+        const int zn = (dc | (s != 0)) ? zpos + 1 : (r == 15 ? z + 16 : 64);
         const int n = len + s;
         p += n;
-        win.consume(words, n);
-        if (z >= 64) {
-            z = 0;
-            done++;
-            blk++;
-            out += 64;
-            c = (c + 1 == bpm) ? 0 : c + 1;
-            tabs = s_tab + ((ncomp == 1 || c < luma) ? 0 : c - luma + 1) * 2;
+        const bool eob = zn >= 64;
+        z = eob ? 0 : zn;
+        done += eob ? 1 : 0;
+        if (WRITE) {
+            blk += eob ? 1 : 0;
+            out += eob ? 64 : 0;
         }
+        c = eob ? ((c + 1 == bpm) ? 0 : c + 1) : c;
+        comp2 = (ncomp == 1 || c < luma) ? 0 : 2 * (c - luma + 1);
     }
     cur.p = p;
     cur.c = c;
@@ -178,6 +153,7 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, C
     return done;
 }
 
+template <int kEntropyThreads>
 __global__ void __launch_bounds__(kEntropyThreads)
 entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
                         const uint8_t *__restrict__ blob, const HuffTable *__restrict__ huff,
@@ -226,13 +202,14 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         }
         int total;
         int off = block_scan_exclusive(__popc(keep), s_warp, total);
-        uint8_t *o = cl + clean_len + off;
+        // byte k of the stream lives at address k ^ 3: every 32-bit word holds its bits MSB first
+        uint32_t o = clean_len + off;
 #pragma unroll
         for (int i = 0; i < 16; i++)
-            if (keep & (1u << i)) *o++ = b[i];
+            if (keep & (1u << i)) cl[(o++) ^ 3u] = b[i];
         clean_len += total;
     }
-    if (tid < 32) cl[clean_len + tid] = 0;
+    if (tid < 32) cl[(clean_len + tid) ^ 3u] = 0;
     __syncthreads();
 
     const uint32_t *words = reinterpret_cast<const uint32_t *>(cl);
@@ -442,10 +419,26 @@ __global__ void entropy_sequential_kernel(const ImageDesc *__restrict__ descs,
 void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
                            const int32_t *seq_list, int n_seq, const uint8_t *blob,
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
-                           int subseq_bits, cudaStream_t stream) {
-    if (n_list > 0)
-        entropy_parallel_kernel<<<n_list, kEntropyThreads, 0, stream>>>(descs, list, blob, huff, clean,
-                                                                        coef, status, subseq_bits);
+                           int subseq_bits, int entropy_threads, cudaStream_t stream) {
+    if (n_list > 0) {
+        switch (entropy_threads) {
+        case 128:
+            entropy_parallel_kernel<128><<<n_list, 128, 0, stream>>>(descs, list, blob, huff, clean, coef, status,
+                                                                     subseq_bits);
+            break;
+        case 256:
+            entropy_parallel_kernel<256><<<n_list, 256, 0, stream>>>(descs, list, blob, huff, clean, coef, status,
+                                                                     subseq_bits);
+            break;
+        case 1024:
+            entropy_parallel_kernel<1024><<<n_list, 1024, 0, stream>>>(descs, list, blob, huff, clean, coef, status,
+                                                                       subseq_bits);
+            break;
+        default:
+            entropy_parallel_kernel<512><<<n_list, 512, 0, stream>>>(descs, list, blob, huff, clean, coef, status,
+                                                                     subseq_bits);
+        }
+    }
     if (n_seq > 0)
         entropy_sequential_kernel<<<(n_seq + 31) / 32, 32, 0, stream>>>(descs, seq_list, n_seq, blob,
                                                                         huff, coef, status);

@@ -141,36 +141,6 @@ __device__ __forceinline__ int chroma_sample(const uint8_t *__restrict__ p, int 
     return (cur * 3 + 3 * row[cx + 1] + far[cx + 1] + 7) >> 4;
 }
 
-__global__ void __launch_bounds__(256)
-color_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
-             const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb) {
-    const ImageDesc &d = descs[list[blockIdx.y]];
-    if (d.host_status != 0) return;
-    const int W = d.width, H = d.height;
-    const int npix = W * H;
-    const int yw = d.mcus_x * d.hs * 8, cw = d.mcus_x * 8;
-    const int real_w = (W + d.hs - 1) / d.hs, real_h = (H + d.vs - 1) / d.vs;
-    const uint8_t *Y = planes + d.plane_off[0];
-    const uint8_t *Cb = planes + d.plane_off[1];
-    const uint8_t *Cr = planes + d.plane_off[2];
-    uint8_t *out = rgb + d.rgb_off;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < npix; i += gridDim.x * blockDim.x) {
-        const int y = i / W, x = i - y * W;
-        const int lum = Y[(size_t)y * yw + x];
-        int r = lum, g = lum, b = lum;
-        if (d.ncomp == 3) {
-            const int cb = chroma_sample(Cb, cw, real_w, real_h, d.hs, d.vs, x, y) - 128;
-            const int cr = chroma_sample(Cr, cw, real_w, real_h, d.hs, d.vs, x, y) - 128;
-            r = lum + ((91881 * cr + 32768) >> 16);
-            g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
-            b = lum + ((116130 * cb + 32768) >> 16);
-        }
-        out[(size_t)i * 3 + 0] = (uint8_t)min(255, max(0, r));
-        out[(size_t)i * 3 + 1] = (uint8_t)min(255, max(0, g));
-        out[(size_t)i * 3 + 2] = (uint8_t)min(255, max(0, b));
-    }
-}
-
 // ------------------------------------------------------------------------------------------
 // Payload gather from pinned host memory, so that the host CPU never touches the sample bytes.
 // 16 CTAs of 256 threads with four 16-byte loads in flight each (256 KB outstanding) already fill
@@ -217,14 +187,113 @@ void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32
                                                                coef, planes);
 }
 
-void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int max_pixels,
-                  const uint8_t *planes, uint8_t *rgb, cudaStream_t stream) {
+// 4:2:0 images: one thread per chroma sample = 2 x 2 output pixels.  The triangle filter of the
+// four pixels reads the same 3 x 3 chroma neighbourhood (image edges replicate, which is what
+// the filter's edge formulas amount to), so the neighbourhood is loaded once: ~40 instructions
+// per pixel instead of ~240.  Only the chroma cells the crop box touches are converted.
+__global__ void __launch_bounds__(256)
+color_quad_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
+                  const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb,
+                  const int32_t *__restrict__ params, int n_params) {
+    const int img = list[blockIdx.z];
+    const ImageDesc &d = descs[img];
+    if (d.host_status != 0 || d.ncomp != 3 || d.hs != 2 || d.vs != 2) return;
+    const int W = d.width, H = d.height;
+    const int real_w = (W + 1) >> 1, real_h = (H + 1) >> 1;
+    if (real_w < 3) return; // too narrow for the filter: the per-pixel kernel replicates
+    int x0 = 0, y0 = 0, x1 = W, y1 = H; // pixel box to convert
+    if (params) {
+        const int32_t *p = params + (size_t)img * n_params;
+        if (p[2] > 0 && p[3] > 0 && p[0] >= 0 && p[1] >= 0 && p[0] + p[2] <= H && p[1] + p[3] <= W) {
+            y0 = p[0];
+            x0 = p[1];
+            y1 = p[0] + p[2];
+            x1 = p[1] + p[3];
+        }
+    }
+    const int cx = (x0 >> 1) + blockIdx.x * 32 + threadIdx.x;
+    const int cy = (y0 >> 1) + blockIdx.y * 8 + threadIdx.y;
+    if (cx > ((x1 - 1) >> 1) || cy > ((y1 - 1) >> 1)) return;
+    const int yw = d.mcus_x * 16, cw = d.mcus_x * 8;
+    const int xl = max(cx - 1, 0), xr = min(cx + 1, real_w - 1);
+    const int yu = max(cy - 1, 0), yd = min(cy + 1, real_h - 1);
+    int cval[2][4]; // [Cb, Cr][upper-left, upper-right, lower-left, lower-right]
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const uint8_t *P = planes + d.plane_off[1 + k];
+        const uint8_t *ru = P + (size_t)yu * cw, *rc = P + (size_t)cy * cw, *rd = P + (size_t)yd * cw;
+        const int cl = rc[xl], cc = rc[cx], cr = rc[xr];
+        const int ul = 3 * cl + ru[xl], uc = 3 * cc + ru[cx], ur = 3 * cr + ru[xr]; // towards the row above
+        const int dl = 3 * cl + rd[xl], dc = 3 * cc + rd[cx], dr = 3 * cr + rd[xr]; // towards the row below
+        cval[k][0] = (3 * uc + ul + 8) >> 4;
+        cval[k][1] = (3 * uc + ur + 7) >> 4;
+        cval[k][2] = (3 * dc + dl + 8) >> 4;
+        cval[k][3] = (3 * dc + dr + 7) >> 4;
+    }
+    const uint8_t *Y = planes + d.plane_off[0];
+    uint8_t *out = rgb + d.rgb_off;
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int x = 2 * cx + (q & 1), y = 2 * cy + (q >> 1);
+        if (x >= W || y >= H) continue;
+        const int lum = Y[(size_t)y * yw + x];
+        const int cb = cval[0][q] - 128, cr = cval[1][q] - 128;
+        const int r = lum + ((91881 * cr + 32768) >> 16);
+        const int g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
+        const int b = lum + ((116130 * cb + 32768) >> 16);
+        uint8_t *o = out + ((size_t)y * W + x) * 3;
+        o[0] = (uint8_t)min(255, max(0, r));
+        o[1] = (uint8_t)min(255, max(0, g));
+        o[2] = (uint8_t)min(255, max(0, b));
+    }
+}
+
+// Per-pixel kernel for everything the quad kernel leaves out (4:4:4, 4:2:2, greyscale, images
+// narrower than the triangle filter).
+__global__ void __launch_bounds__(256)
+color_other_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
+                   const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb) {
+    const ImageDesc &d = descs[list[blockIdx.y]];
+    if (d.host_status != 0) return;
+    const int W = d.width, H = d.height;
+    const int real_w = (W + d.hs - 1) / d.hs, real_h = (H + d.vs - 1) / d.vs;
+    if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && real_w >= 3) return; // quad kernel's
+    const int npix = W * H;
+    const int yw = d.mcus_x * d.hs * 8, cw = d.mcus_x * 8;
+    const uint8_t *Y = planes + d.plane_off[0];
+    const uint8_t *Cb = planes + d.plane_off[1];
+    const uint8_t *Cr = planes + d.plane_off[2];
+    uint8_t *out = rgb + d.rgb_off;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < npix; i += gridDim.x * blockDim.x) {
+        const int y = i / W, x = i - y * W;
+        const int lum = Y[(size_t)y * yw + x];
+        int r = lum, g = lum, b = lum;
+        if (d.ncomp == 3) {
+            const int cb = chroma_sample(Cb, cw, real_w, real_h, d.hs, d.vs, x, y) - 128;
+            const int cr = chroma_sample(Cr, cw, real_w, real_h, d.hs, d.vs, x, y) - 128;
+            r = lum + ((91881 * cr + 32768) >> 16);
+            g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
+            b = lum + ((116130 * cb + 32768) >> 16);
+        }
+        out[(size_t)i * 3 + 0] = (uint8_t)min(255, max(0, r));
+        out[(size_t)i * 3 + 1] = (uint8_t)min(255, max(0, g));
+        out[(size_t)i * 3 + 2] = (uint8_t)min(255, max(0, b));
+    }
+}
+
+void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n_quad, int n_other,
+                  int max_w, int max_h, const uint8_t *planes, uint8_t *rgb, const int32_t *crop_params,
+                  int n_params, cudaStream_t stream) {
     if (n_list == 0) return;
-    int bx = (max_pixels + 256 * 4 - 1) / (256 * 4);
-    if (bx < 1) bx = 1;
-    if (bx > 1024) bx = 1024;
-    dim3 grid(bx, n_list);
-    color_kernel<<<grid, 256, 0, stream>>>(descs, list, planes, rgb);
+    if (n_quad > 0) {
+        dim3 grid(((max_w + 1) / 2 + 31) / 32, ((max_h + 1) / 2 + 7) / 8, n_list);
+        color_quad_kernel<<<grid, dim3(32, 8), 0, stream>>>(descs, list, planes, rgb, crop_params, n_params);
+    }
+    if (n_other > 0) {
+        int bx = (max_w * max_h + 256 * 4 - 1) / (256 * 4);
+        bx = bx < 1 ? 1 : (bx > 1024 ? 1024 : bx);
+        color_other_kernel<<<dim3(bx, n_list), 256, 0, stream>>>(descs, list, planes, rgb);
+    }
 }
 
 } // namespace ffcvb

@@ -124,11 +124,34 @@ void build_huff_table(const RawHuff &raw, HuffTable *t) {
     t->maxcode[17] = 0x7fffffff;
     code = 0;
     k = 0;
-    for (int len = 1; len <= 9; len++) {
+    int n_sub = 0;
+    int sub_of_prefix[512];
+    for (int i = 0; i < 512; i++) sub_of_prefix[i] = -1;
+    for (int len = 1; len <= 16; len++) {
         for (int i = 0; i < raw.bits[len]; i++, k++, code++) {
-            int first = code << (9 - len);
-            for (int f = 0; f < (1 << (9 - len)); f++)
-                t->look[first + f] = (uint16_t)((len << 8) | raw.vals[k]);
+            if (code >= (1 << len)) continue; // over-subscribed table: ignore the excess codes
+            const uint16_t entry = (uint16_t)((len << 8) | raw.vals[k]);
+            if (len <= 9) {
+                const int first = code << (9 - len);
+                for (int f = 0; f < (1 << (9 - len)); f++) t->look[first + f] = entry;
+            } else {
+                const int prefix = code >> (len - 9);
+                if (sub_of_prefix[prefix] < 0) {
+                    if (n_sub < kHuffSubTables) {
+                        sub_of_prefix[prefix] = n_sub;
+                        t->look[prefix] = (uint16_t)(0x8000 | n_sub);
+                        n_sub++;
+                    } else {
+                        sub_of_prefix[prefix] = kHuffSubTables; // no room: this prefix walks the code lengths
+                        t->look[prefix] = 0xFFFF;
+                    }
+                }
+                const int sub = sub_of_prefix[prefix];
+                if (sub < kHuffSubTables) {
+                    const int rest = (code << (16 - len)) & 127; // bits 10..16, left-aligned
+                    for (int f = 0; f < (1 << (16 - len)); f++) t->sub[sub][rest + f] = entry;
+                }
+            }
         }
         code <<= 1;
     }

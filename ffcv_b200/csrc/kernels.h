@@ -15,19 +15,24 @@ void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, cudaSt
 // into `clean`, Huffman-decodes it into quantised coefficients (natural order inside a block,
 // blocks in scan order, DC un-differenced) in `coef`, and records a per-sample status.
 // `subseq_bits` is the length of the subsequences decoded speculatively in parallel (multiple
-// of 32).  `coef` must be zeroed by the caller.
+// of 32), `entropy_threads` (128, 256, 512 or 1024) the CTA size: one CTA decodes one image,
+// `entropy_threads` subsequences at a time.  `coef` must be zeroed by the caller.
 void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
                            const int32_t *seq_list, int n_seq, const uint8_t *blob,
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
-                           int subseq_bits, cudaStream_t stream);
+                           int subseq_bits, int entropy_threads, cudaStream_t stream);
 
 // Dequantise + fast integer IDCT of `total_blocks` blocks into the 8-bit component planes.
 void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32_t total_blocks,
                  const MultTable *mult, const int16_t *coef, uint8_t *planes, cudaStream_t stream);
 
-// Chroma upsampling (triangle filter) + YCbCr->RGB into packed h*w*3 images in `rgb`.
-void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int max_pixels,
-                  const uint8_t *planes, uint8_t *rgb, cudaStream_t stream);
+// Chroma upsampling (triangle filter) + YCbCr->RGB into packed h*w*3 images in `rgb`.  4:2:0
+// images (n_quad of them) go through the 2x2-quad kernel, which converts only the crop box given
+// by `crop_params` (row, col, h, w per sample; nullptr = whole image); the other n_other images go
+// through the per-pixel kernel.  max_w / max_h bound the image sizes in the list.
+void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n_quad, int n_other,
+                  int max_w, int max_h, const uint8_t *planes, uint8_t *rgb, const int32_t *crop_params,
+                  int n_params, cudaStream_t stream);
 
 // Source of the fused kernel.
 struct ResizeSource {

@@ -29,7 +29,7 @@ constexpr size_t kMaxStreamBytes = FFCVB_STATIC_MAX_STREAM_BYTES;    // compress
 constexpr size_t kMaxPaddedSamples = FFCVB_STATIC_MAX_PADDED_PIXELS; // per component, padded to MCUs
 
 // Scratch layout inside the static array (all offsets multiples of 256).
-constexpr size_t kMetaBytes = 16 * 1024;                             // descriptor, tables, list, status
+constexpr size_t kMetaBytes = 48 * 1024;                             // descriptor, tables, list, status
 constexpr size_t kCleanBytes = kMaxStreamBytes + 256;                // unstuffed bit stream
 constexpr size_t kCoefBytes = 3 * kMaxPaddedSamples * sizeof(int16_t); // 64 coefficients per 64 samples
 constexpr size_t kPlaneBytes = 3 * kMaxPaddedSamples + 1024;         // each plane rounded up to 256
@@ -137,10 +137,12 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     subseq = subseq < 512 ? 512 : (subseq > 2048 ? 2048 : subseq);
     launch_entropy_decode(desc_dev, list_dev, sequential ? 0 : 1, list_dev, sequential ? 1 : 0, jpeg_dev, meta_dev->huff,
                           scratch + kCleanOff, reinterpret_cast<int16_t *>(scratch + kCoefOff), meta_dev->status,
-                          (int)subseq, st);
+                          (int)subseq, 512, st);
     launch_idct(desc_dev, list_dev, 1, d.nblocks, meta_dev->mult, reinterpret_cast<const int16_t *>(scratch + kCoefOff),
                 scratch + kPlaneOff, st);
-    launch_color(desc_dev, list_dev, 1, (int)(height * width), scratch + kPlaneOff, rgb_dev, st);
+    const bool quad = d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (width + 1) / 2 >= 3;
+    launch_color(desc_dev, list_dev, 1, quad ? 1 : 0, quad ? 0 : 1, (int)width, (int)height, scratch + kPlaneOff,
+                 rgb_dev, nullptr, 0, st);
     if (cudaGetLastError() != cudaSuccess) return reject(FFCVB_E_CUDA, "kernel launch failed");
     return FFCVB_OK;
 }

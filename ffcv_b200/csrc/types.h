@@ -37,9 +37,15 @@ struct ImageDesc {
 };
 
 // Canonical Huffman code (ITU-T T.81 Annex C) prepared for table-driven decoding.
+constexpr int kHuffSubTables = 16;
 struct HuffTable {
-    uint16_t look[512];  // 9-bit look-ahead: (code length << 8) | symbol; 0 when the code is longer
-    int32_t maxcode[18]; // largest code of each length (left-aligned compare is done by the reader)
+    // First level, indexed by the next 9 bits: (code length << 8) | symbol for codes of up to 9
+    // bits; 0x8000 | k when the code is longer and continues in sub[k]; 0xFFFF when it is longer
+    // and no sub-table was left (walk maxcode/valoff instead); 0 for an invalid prefix.
+    uint16_t look[512];
+    // Second level, indexed by bits 10..16 of the code: (code length << 8) | symbol, 0 if invalid.
+    uint16_t sub[kHuffSubTables][128];
+    int32_t maxcode[18]; // largest code of each length, -1 if none
     int32_t valoff[17];  // index of the first symbol of each length minus its first code
     uint8_t vals[256];
 };

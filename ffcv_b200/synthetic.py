@@ -87,23 +87,34 @@ class SyntheticImageDataset:
         return img, label
 
 
+def _field_444_class():
+    from .fields import RGBImageField
+
+    class RGBImageField444(RGBImageField):
+        """Same metadata and payload kinds; JPEG written without chroma subsampling."""
+
+        def encode_jpeg(self, image):
+            import cv2
+            ok, res = cv2.imencode('.jpg', cv2.cvtColor(image, cv2.COLOR_RGB2BGR),
+                                   [int(cv2.IMWRITE_JPEG_QUALITY), self.jpeg_quality,
+                                    int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR), int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444)])
+            if not ok:
+                raise ValueError("Impossible to encode image in jpeg")
+            return res.reshape(-1)
+    return RGBImageField444
+
+
+RGBImageField444 = None
+
+
 def make_field(cfg_id):
     from .fields import RGBImageField
+    global RGBImageField444
     cfg = CONFIGS[cfg_id]
     if cfg.get('sampling') == 444:
-        import cv2
-
-        class RGBImageField444(RGBImageField):
-            """Same metadata and payload kinds; JPEG written without chroma subsampling."""
-
-            def encode_jpeg(self, image):
-                ok, res = cv2.imencode('.jpg', cv2.cvtColor(image, cv2.COLOR_RGB2BGR),
-                                       [int(cv2.IMWRITE_JPEG_QUALITY), self.jpeg_quality,
-                                        int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR),
-                                        int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444)])
-                if not ok:
-                    raise ValueError("Impossible to encode image in jpeg")
-                return res.reshape(-1)
+        if RGBImageField444 is None:
+            RGBImageField444 = _field_444_class()
+            RGBImageField444.__qualname__ = 'RGBImageField444'  # picklable by module attribute
         return RGBImageField444(**cfg['field'])
     return RGBImageField(**cfg['field'])
 
