@@ -6,7 +6,8 @@
 // is cut into fixed-length subsequences, every thread decodes its subsequence from a guessed
 // state, and the guesses are repaired by re-decoding from the left neighbour's exit state until
 // no input changes (a Jacobi iteration on a chain whose first link is exact, so it converges in
-// a few rounds in practice and in at most one round per thread in the worst case).  A prefix sum
+// a few rounds in practice -- about 7 kbit of stream, dominated by the block's slot inside the
+// MCU -- and in at most one round per subsequence in the worst case).  A prefix sum
 // of completed blocks then gives every thread its output position and a last pass writes the
 // coefficients.  DC differences are integrated per component by a block-wide scan.
 //
@@ -161,6 +162,9 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
                         int32_t *__restrict__ status, int subseq_bits) {
     __shared__ HuffTable s_tab[6];
     __shared__ unsigned long long s_state[kEntropyThreads + 1];
+    __shared__ uint16_t s_blocks[kEntropyThreads]; // blocks completed inside each subsequence
+    __shared__ uint16_t s_list[kEntropyThreads];   // compacted indices of the dirty subsequences
+    __shared__ uint8_t s_dirty[kEntropyThreads + 1];
     __shared__ int s_warp[33];
     __shared__ uint8_t s_zz[64];
 
@@ -235,23 +239,42 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         if (sub_end > total_bits) sub_end = total_bits;
         Cursor guess = {sub_start, 0, 0};
         s_state[tid] = tid == 0 ? carry : pack(guess);
-        unsigned long long last_in = ~0ull;
-        int my_blocks = 0;
+        s_dirty[tid] = 1;
+        s_blocks[tid] = 0;
         __syncthreads();
+        // Repair rounds.  A subsequence is dirty when its entry state changed since it was last
+        // decoded.  Dirty subsequences are compacted each round so that the work fills
+        // whole warps (after the first rounds only a minority is dirty) and idle warps only meet
+        // at the barriers.
         for (int iter = 0; iter <= nsub; iter++) {
-            const unsigned long long in = s_state[tid];
+            const bool dirty = active && s_dirty[tid];
+            int n_dirty;
+            const int pos = block_scan_exclusive(dirty ? 1 : 0, s_warp, n_dirty);
+            if (n_dirty == 0) break;
+            if (dirty) s_list[pos] = (uint16_t)tid;
             __syncthreads();
-            int changed = 0;
-            if (active && in != last_in) {
-                Cursor cur = unpack(in);
-                my_blocks = decode_span<false>(words, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz,
-                                               nullptr, 0, 0);
-                s_state[tid + 1] = pack(cur);
-                last_in = in;
-                changed = 1;
+            int t = -1;
+            unsigned long long in = 0;
+            if (tid < n_dirty) {
+                t = s_list[tid];
+                in = s_state[t];
+                s_dirty[t] = 0; // cleared before the barrier, set again (by the left neighbour) only after it
             }
-            if (!__syncthreads_or(changed)) break;
+            __syncthreads(); // every entry state is read before any exit state is written
+            if (t >= 0) {
+                Cursor cur = unpack(in);
+                uint32_t t_end = (first_sub + (uint32_t)t + 1) * S;
+                if (t_end > total_bits) t_end = total_bits;
+                s_blocks[t] = (uint16_t)decode_span<false>(words, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
+                const unsigned long long out = pack(cur);
+                if (s_state[t + 1] != out) { // only this thread writes entry t + 1 in this round
+                    s_state[t + 1] = out;
+                    s_dirty[t + 1] = 1;
+                }
+            }
+            __syncthreads();
         }
+        const int my_blocks = active ? s_blocks[tid] : 0;
         int chunk_blocks;
         const int first = block_scan_exclusive(my_blocks, s_warp, chunk_blocks);
         if (active) {

@@ -68,6 +68,9 @@ __device__ __forceinline__ void linear_taps(int d, int ssize, double inv, double
 
 __device__ __forceinline__ int sat_round(float v) { return min(255, max(0, __float2int_rn(v))); }
 
+// Exact uint8 -> float without the conversion pipe: 2^23 + v is representable, subtract 2^23.
+__device__ __forceinline__ float u8f(uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.0f; }
+
 // Per-axis tap tables in shared memory, computed once per CTA (double-precision position
 // arithmetic as OpenCV does it, then only fp32 / integer work per pixel).
 struct TapTables {
@@ -99,7 +102,8 @@ __device__ __forceinline__ void fill_taps(const TapTables &t, int k, int d, int 
 
 template <typename OutT>
 __global__ void __launch_bounds__(256)
-resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int n_params, OpList ops,
+resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *__restrict__ params, int n_params,
+                      const __grid_constant__ OpList ops,
                       int resize, int out_h, int out_w, int band_rows, int planar,
                       const OutT *__restrict__ lut, OutT *__restrict__ out,
                       const int32_t *__restrict__ status) {
@@ -185,8 +189,9 @@ resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int 
 
     const uint8_t *roi = base + (ptrdiff_t)(ci - row0) * stride + (cj - col0) * 3;
     const int npix = rows * out_w;
+    const uint32_t inv_w = (uint32_t)((0x100000000ull + out_w - 1) / out_w); // pix / out_w for pix < 2^16
     for (int pix = threadIdx.x; pix < npix; pix += blockDim.x) {
-        const int r = pix / out_w, ox = pix - r * out_w, oy = band0 + r;
+        const int r = (int)__umulhi((uint32_t)pix, inv_w), ox = pix - r * out_w, oy = band0 + r;
         // ---- trace the output pixel back through the augmentations
         int y = oy, x = ox;
         bool filled = false;
@@ -248,9 +253,9 @@ resize_augment_kernel(ResizeSource src, const int32_t *__restrict__ params, int 
                     float r0 = 0.f, r1 = 0.f, r2 = 0.f;
                     for (int k = 0; k < xn; k++, p += 3) {
                         const float w = (k == 0 && xl) ? xwl : ((k == xn - 1 && xr) ? xwr : xwm);
-                        r0 = __fadd_rn(r0, __fmul_rn((float)p[0], w));
-                        r1 = __fadd_rn(r1, __fmul_rn((float)p[1], w));
-                        r2 = __fadd_rn(r2, __fmul_rn((float)p[2], w));
+                        r0 = __fadd_rn(r0, __fmul_rn(u8f(p[0]), w));
+                        r1 = __fadd_rn(r1, __fmul_rn(u8f(p[1]), w));
+                        r2 = __fadd_rn(r2, __fmul_rn(u8f(p[2]), w));
                     }
                     const float beta = (j == 0 && yl) ? ywl : ((j == yn - 1 && yr) ? ywr : ywm);
                     if (j == 0) {
