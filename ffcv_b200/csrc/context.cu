@@ -244,12 +244,13 @@ OpList make_oplist(const ffcvb_plan &p) {
 }
 
 int pick_subseq_bits(size_t max_scan_bytes) {
-    // One pass of the 512 decoder threads should cover the largest image of the batch; the
-    // decoder needs about 7 kbit to re-synchronise, so shorter subsequences only add repair
-    // rounds and longer ones leave threads idle.
-    size_t s = align_up(max_scan_bytes * 8 / 512 + 1, 32);
+    // One pass of the 512 decoder threads should cover the largest image of the batch (the decoder
+    // needs about 7 kbit to re-synchronise, so shorter subsequences only add repair rounds), but a
+    // chunk of 512 subsequences must also fit shared memory twice per SM: at most 1280 bits
+    // (80 KB per CTA).  Multiples of 128 bits keep chunk starts 16-byte aligned.
+    size_t s = align_up(max_scan_bytes * 8 / 512 + 1, 128);
     if (s < 512) s = 512;
-    if (s > 2048) s = 2048;
+    if (s > 1280) s = 1280;
     return (int)s;
 }
 
@@ -437,7 +438,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         d.block_base = total_blocks;
         total_blocks += d.nblocks;
         d.clean_off = clean_bytes;
-        clean_bytes += align_up((size_t)d.scan_len + 48, 16);
+        clean_bytes += align_up((size_t)d.scan_len + 96, 16);
         for (int c = 0; c < h.ncomp; c++) {
             d.plane_off[c] = plane_bytes;
             const size_t pw = (size_t)d.mcus_x * (c == 0 ? d.hs : 1) * 8;
@@ -550,9 +551,10 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.subseq_bits = pick_subseq_bits(scan_bytes_par);
     s.entropy_threads = 512;
     // tuning overrides
-    if (const char *e = getenv("FFCV_B200_SUBSEQ_BITS")) s.subseq_bits = (atoi(e) + 31) / 32 * 32;
+    if (const char *e = getenv("FFCV_B200_SUBSEQ_BITS")) s.subseq_bits = (atoi(e) + 127) / 128 * 128;
     if (const char *e = getenv("FFCV_B200_ENTROPY_THREADS")) s.entropy_threads = atoi(e);
-    if (s.subseq_bits < 64) s.subseq_bits = 64;
+    if (s.subseq_bits < 128) s.subseq_bits = 128;
+    while ((size_t)s.entropy_threads * s.subseq_bits / 8 > 160 * 1024) s.subseq_bits -= 128; // shared-memory limit
     s.scan_bytes = s.raw_bytes = s.jpeg_bytes = 0;
     for (int i = 0; i < n; i++) {
         if (descs[i].mode == FFCVB_MODE_JPG) {

@@ -108,11 +108,12 @@ __device__ __forceinline__ Cursor unpack(uint64_t v) {
 
 // Decodes symbols from `cur` until its position reaches `end`.  Returns the number of blocks
 // completed.  With WRITE, coefficients go to cf (image base) starting at block `blk`.
+// `words` holds the stream from bit `bit_base` on (the chunk's copy in shared memory).
 // The 32 lanes of a warp walk unrelated parts of the stream, so the step is written as straight
 // line code with selects (DC / AC / end-of-block / zero-run / block end all take the same path);
 // codes longer than the 9-bit first-level table cost one more table read.
 template <bool WRITE>
-__device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, Cursor &cur,
+__device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, uint32_t bit_base, Cursor &cur,
                                            uint32_t end, int bpm, int luma, int ncomp,
                                            const HuffTable *s_tab, const uint8_t *s_zz,
                                            int16_t *__restrict__ cf, uint32_t blk,
@@ -123,7 +124,7 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, C
     int comp2 = (ncomp == 1 || c < luma) ? 0 : 2 * (c - luma + 1);
     int16_t *out = cf + (size_t)blk * 64;
     while (p < end) {
-        const uint32_t w = peek32(words, p);
+        const uint32_t w = peek32(words, p - bit_base);
         const bool dc = z == 0;
         const HuffTable &t = s_tab[comp2 + (dc ? 0 : 1)];
         int len, sym;
@@ -160,6 +161,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
                         const uint8_t *__restrict__ blob, const HuffTable *__restrict__ huff,
                         uint8_t *__restrict__ clean, int16_t *__restrict__ coef,
                         int32_t *__restrict__ status, int subseq_bits) {
+    extern __shared__ __align__(16) uint32_t s_stream[]; // this chunk of the unstuffed stream
     __shared__ HuffTable s_tab[6];
     __shared__ unsigned long long s_state[kEntropyThreads + 1];
     __shared__ uint16_t s_blocks[kEntropyThreads]; // blocks completed inside each subsequence
@@ -213,7 +215,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
             if (keep & (1u << i)) cl[(o++) ^ 3u] = b[i];
         clean_len += total;
     }
-    if (tid < 32) cl[(clean_len + tid) ^ 3u] = 0;
+    if (tid < 64) cl[(clean_len + tid) ^ 3u] = 0;
     __syncthreads();
 
     const uint32_t *words = reinterpret_cast<const uint32_t *>(cl);
@@ -237,6 +239,18 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         const uint32_t sub_start = g * S;
         uint32_t sub_end = sub_start + S;
         if (sub_end > total_bits) sub_end = total_bits;
+        // The chunk's bits go to shared memory: every lane of a warp reads a different part of the
+        // stream for every symbol, which shared memory serves at a few cycles per warp while the
+        // same pattern on global memory saturates the L1 tag stage (one sector lookup per cycle).
+        const uint32_t bit_base = first_sub * S; // S is a multiple of 128: 16-byte aligned in the stream
+        {
+            uint32_t n16 = ((uint32_t)nsub * S + 127) / 128 + 1; // one vector of overrun for the last symbol
+            const uint32_t have16 = (clean_len + 64 - (bit_base >> 3)) / 16; // zero padding included
+            if (n16 > have16) n16 = have16;
+            const uint4 *src16 = reinterpret_cast<const uint4 *>(words + (bit_base >> 5));
+            uint4 *dst16 = reinterpret_cast<uint4 *>(s_stream);
+            for (uint32_t k = tid; k < n16; k += kEntropyThreads) dst16[k] = src16[k];
+        }
         Cursor guess = {sub_start, 0, 0};
         s_state[tid] = tid == 0 ? carry : pack(guess);
         s_dirty[tid] = 1;
@@ -265,7 +279,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
                 Cursor cur = unpack(in);
                 uint32_t t_end = (first_sub + (uint32_t)t + 1) * S;
                 if (t_end > total_bits) t_end = total_bits;
-                s_blocks[t] = (uint16_t)decode_span<false>(words, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
+                s_blocks[t] = (uint16_t)decode_span<false>(s_stream, bit_base, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
                 const unsigned long long out = pack(cur);
                 if (s_state[t + 1] != out) { // only this thread writes entry t + 1 in this round
                     s_state[t + 1] = out;
@@ -279,7 +293,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         const int first = block_scan_exclusive(my_blocks, s_warp, chunk_blocks);
         if (active) {
             Cursor cur = unpack(s_state[tid]);
-            decode_span<true>(words, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
+            decode_span<true>(s_stream, bit_base, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
                               blk_base + (uint32_t)first, d.nblocks);
         }
         carry = s_state[nsub];
@@ -444,22 +458,16 @@ void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_li
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
                            int subseq_bits, int entropy_threads, cudaStream_t stream) {
     if (n_list > 0) {
+        auto launch = [&](auto kernel, int threads) {
+            const size_t smem = ((size_t)threads * subseq_bits / 8 + 63) / 16 * 16 + 16;
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<n_list, threads, smem, stream>>>(descs, list, blob, huff, clean, coef, status, subseq_bits);
+        };
         switch (entropy_threads) {
-        case 128:
-            entropy_parallel_kernel<128><<<n_list, 128, 0, stream>>>(descs, list, blob, huff, clean, coef, status,
-                                                                     subseq_bits);
-            break;
-        case 256:
-            entropy_parallel_kernel<256><<<n_list, 256, 0, stream>>>(descs, list, blob, huff, clean, coef, status,
-                                                                     subseq_bits);
-            break;
-        case 1024:
-            entropy_parallel_kernel<1024><<<n_list, 1024, 0, stream>>>(descs, list, blob, huff, clean, coef, status,
-                                                                       subseq_bits);
-            break;
-        default:
-            entropy_parallel_kernel<512><<<n_list, 512, 0, stream>>>(descs, list, blob, huff, clean, coef, status,
-                                                                     subseq_bits);
+        case 128: launch(entropy_parallel_kernel<128>, 128); break;
+        case 256: launch(entropy_parallel_kernel<256>, 256); break;
+        case 1024: launch(entropy_parallel_kernel<1024>, 1024); break;
+        default: launch(entropy_parallel_kernel<512>, 512);
         }
     }
     if (n_seq > 0)

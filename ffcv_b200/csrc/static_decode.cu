@@ -30,7 +30,7 @@ constexpr size_t kMaxPaddedSamples = FFCVB_STATIC_MAX_PADDED_PIXELS; // per comp
 
 // Scratch layout inside the static array (all offsets multiples of 256).
 constexpr size_t kMetaBytes = 48 * 1024;                             // descriptor, tables, list, status
-constexpr size_t kCleanBytes = kMaxStreamBytes + 256;                // unstuffed bit stream
+constexpr size_t kCleanBytes = kMaxStreamBytes + 512;                // unstuffed bit stream
 constexpr size_t kCoefBytes = 3 * kMaxPaddedSamples * sizeof(int16_t); // 64 coefficients per 64 samples
 constexpr size_t kPlaneBytes = 3 * kMaxPaddedSamples + 1024;         // each plane rounded up to 256
 constexpr size_t kCleanOff = kMetaBytes;
@@ -133,8 +133,8 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     const int32_t *list_dev = meta_dev->list; // {0}: the only image
     const bool sequential = d.restart_interval != 0;
     const size_t max_scan = d.scan_len;
-    size_t subseq = ((max_scan * 8 / 512 + 1) + 31) / 32 * 32;
-    subseq = subseq < 512 ? 512 : (subseq > 2048 ? 2048 : subseq);
+    size_t subseq = ((max_scan * 8 / 512 + 1) + 127) / 128 * 128;
+    subseq = subseq < 512 ? 512 : (subseq > 1280 ? 1280 : subseq);
     launch_entropy_decode(desc_dev, list_dev, sequential ? 0 : 1, list_dev, sequential ? 1 : 0, jpeg_dev, meta_dev->huff,
                           scratch + kCleanOff, reinterpret_cast<int16_t *>(scratch + kCoefOff), meta_dev->status,
                           (int)subseq, 512, st);

@@ -37,7 +37,7 @@ struct ImageDesc {
 };
 
 // Canonical Huffman code (ITU-T T.81 Annex C) prepared for table-driven decoding.
-constexpr int kHuffSubTables = 16;
+constexpr int kHuffSubTables = 8; // the standard tables need 5; others fall back to the code-length walk
 struct HuffTable {
     // First level, indexed by the next 9 bits: (code length << 8) | symbol for codes of up to 9
     // bits; 0x8000 | k when the code is longer and continues in sub[k]; 0xFFFF when it is longer
