@@ -135,7 +135,7 @@ struct Slot {
     BatchHeader hdr{};
     ffcvb_plan plan{};
     int n = 0, n_jpeg = 0, n_par = 0, n_seq = 0, max_pixels = 0, subseq_bits = 512, entropy_threads = 512;
-    int n_quad = 0, n_other = 0, max_w = 0, max_h = 0;
+    int n_quad = 0, n_444 = 0, n_other = 0, max_w = 0, max_h = 0;
     uint64_t jpeg_list_off = 0, par_list_off = 0, seq_list_off = 0;
     uint32_t total_blocks = 0;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes = 0, raw_bytes = 0, jpeg_bytes = 0;
@@ -398,7 +398,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     std::vector<int32_t> jpeg_list, par_list, seq_list;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes_par = 0;  // scan_bytes_par: largest scan
     uint32_t total_blocks = 0;
-    int max_pixels = 0, max_w = 0, max_h = 0, n_quad = 0, n_other = 0;
+    int max_pixels = 0, max_w = 0, max_h = 0, n_quad = 0, n_444 = 0, n_other = 0;
     for (int i = 0; i < n; i++) {
         ImageDesc &d = descs[i];
         if (d.mode != FFCVB_MODE_JPG) continue;
@@ -452,6 +452,8 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         if (d.height > max_h) max_h = d.height;
         if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3)
             n_quad++;
+        else if (d.ncomp == 3 && d.hs == 1 && d.vs == 1)
+            n_444++;
         else
             n_other++;
         if (d.restart_interval) {
@@ -544,6 +546,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.max_w = max_w;
     s.max_h = max_h;
     s.n_quad = n_quad;
+    s.n_444 = n_444;
     s.n_other = n_other;
     s.clean_bytes = clean_bytes;
     s.plane_bytes = plane_bytes;
@@ -613,7 +616,7 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         launch_idct(descs, jl, s.n_jpeg, s.total_blocks, mult, (const int16_t *)s.coef.p,
                     (uint8_t *)s.planes.p, st);
         if (prof) CU(cudaEventRecord(s.ev[3], st));
-        launch_color(descs, jl, s.n_jpeg, s.n_quad, s.n_other, s.max_w, s.max_h, (const uint8_t *)s.planes.p,
+        launch_color(descs, jl, s.n_jpeg, s.n_quad, s.n_444, s.n_other, s.max_w, s.max_h, (const uint8_t *)s.planes.p,
                      (uint8_t *)s.rgb.p, s.plan.resize ? params : nullptr, (int)hd.n_params, st);
         if (prof) CU(cudaEventRecord(s.ev[4], st));
     } else if (prof) {
@@ -702,7 +705,7 @@ int ffcvb_batch_launches(const ffcvb_ctx *ctx, int slot) {
     if (!ctx || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return -1;
     const Slot &s = ctx->slots[slot];
     int k = 1 + (s.direct ? 1 : 0); // fused resize/augment/normalise (+ payload gather)
-    if (s.n_jpeg > 0) k += 1 + (s.n_quad > 0) + (s.n_other > 0) + (s.n_par > 0) + (s.n_seq > 0);
+    if (s.n_jpeg > 0) k += 1 + (s.n_quad > 0) + (s.n_444 > 0) + (s.n_other > 0) + (s.n_par > 0) + (s.n_seq > 0);
     return k;
 }
 

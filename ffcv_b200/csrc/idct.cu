@@ -248,7 +248,45 @@ color_quad_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict
     }
 }
 
-// Per-pixel kernel for everything the quad kernel leaves out (4:4:4, 4:2:2, greyscale, images
+// 4:4:4 images: no upsampling, one thread per pixel of the crop box, 2-D tiles (no divisions).
+__global__ void __launch_bounds__(256)
+color_444_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
+                 const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb,
+                 const int32_t *__restrict__ params, int n_params) {
+    const int img = list[blockIdx.z];
+    const ImageDesc &d = descs[img];
+    if (d.host_status != 0 || d.ncomp != 3 || d.hs != 1 || d.vs != 1) return;
+    const int W = d.width, H = d.height;
+    int x0 = 0, y0 = 0, x1 = W, y1 = H;
+    if (params) {
+        const int32_t *p = params + (size_t)img * n_params;
+        if (p[2] > 0 && p[3] > 0 && p[0] >= 0 && p[1] >= 0 && p[0] + p[2] <= H && p[1] + p[3] <= W) {
+            y0 = p[0];
+            x0 = p[1];
+            y1 = p[0] + p[2];
+            x1 = p[1] + p[3];
+        }
+    }
+    const int pw = d.mcus_x * 8;
+    const uint8_t *Y = planes + d.plane_off[0], *Cb = planes + d.plane_off[1], *Cr = planes + d.plane_off[2];
+    uint8_t *out = rgb + d.rgb_off;
+    // every thread walks a column strip so that the grid stays small for very large images
+    const int x = x0 + blockIdx.x * 32 + threadIdx.x;
+    if (x >= x1) return;
+    for (int y = y0 + blockIdx.y * 8 + threadIdx.y; y < y1; y += gridDim.y * 8) {
+        const size_t s = (size_t)y * pw + x;
+        const int lum = Y[s], cb = Cb[s] - 128, cr = Cr[s] - 128;
+        const int r = lum + ((91881 * cr + 32768) >> 16);
+        const int g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
+        const int b = lum + ((116130 * cb + 32768) >> 16);
+        uint8_t *o = out + ((size_t)y * W + x) * 3;
+        o[0] = (uint8_t)min(255, max(0, r));
+        o[1] = (uint8_t)min(255, max(0, g));
+        o[2] = (uint8_t)min(255, max(0, b));
+    }
+}
+
+// Per-pixel kernel for everything the kernels above leave out (4:2:2, greyscale, 4:2:0 images
 // narrower than the triangle filter).
 __global__ void __launch_bounds__(256)
 color_other_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
@@ -258,6 +296,7 @@ color_other_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restric
     const int W = d.width, H = d.height;
     const int real_w = (W + d.hs - 1) / d.hs, real_h = (H + d.vs - 1) / d.vs;
     if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && real_w >= 3) return; // quad kernel's
+    if (d.ncomp == 3 && d.hs == 1 && d.vs == 1) return;                  // 4:4:4 kernel's
     const int npix = W * H;
     const int yw = d.mcus_x * d.hs * 8, cw = d.mcus_x * 8;
     const uint8_t *Y = planes + d.plane_off[0];
@@ -281,10 +320,16 @@ color_other_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restric
     }
 }
 
-void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n_quad, int n_other,
+void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n_quad, int n_444, int n_other,
                   int max_w, int max_h, const uint8_t *planes, uint8_t *rgb, const int32_t *crop_params,
                   int n_params, cudaStream_t stream) {
     if (n_list == 0) return;
+    if (n_444 > 0) {
+        int gy = (max_h + 7) / 8;
+        if (gy > 64) gy = 64;
+        dim3 grid((max_w + 31) / 32, gy, n_list);
+        color_444_kernel<<<grid, dim3(32, 8), 0, stream>>>(descs, list, planes, rgb, crop_params, n_params);
+    }
     if (n_quad > 0) {
         dim3 grid(((max_w + 1) / 2 + 31) / 32, ((max_h + 1) / 2 + 7) / 8, n_list);
         color_quad_kernel<<<grid, dim3(32, 8), 0, stream>>>(descs, list, planes, rgb, crop_params, n_params);

@@ -27,10 +27,10 @@ void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32
                  const MultTable *mult, const int16_t *coef, uint8_t *planes, cudaStream_t stream);
 
 // Chroma upsampling (triangle filter) + YCbCr->RGB into packed h*w*3 images in `rgb`.  4:2:0
-// images (n_quad of them) go through the 2x2-quad kernel, which converts only the crop box given
-// by `crop_params` (row, col, h, w per sample; nullptr = whole image); the other n_other images go
-// through the per-pixel kernel.  max_w / max_h bound the image sizes in the list.
-void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n_quad, int n_other,
+// images (n_quad of them) go through the 2x2-quad kernel and 4:4:4 images (n_444) through a
+// per-pixel 2-D kernel, both converting only the crop box given by `crop_params` (row, col, h, w
+// per sample; nullptr = whole image); the other n_other images go through the generic kernel.  max_w / max_h bound the image sizes in the list.
+void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n_quad, int n_444, int n_other,
                   int max_w, int max_h, const uint8_t *planes, uint8_t *rgb, const int32_t *crop_params,
                   int n_params, cudaStream_t stream);
 

@@ -17,6 +17,7 @@ from .sampling import batch_seed
 class FusedImagePlan:
     def __init__(self):
         self.decoder = None       # the RGB image decoder opening the pipeline
+        self.crop_sampler = None  # operation that draws the crop boxes when it is not the decoder
         self.out_h = self.out_w = None
         self.resize = False
         self.ops = []             # (native type, arg, fill, operation) in pipeline order
@@ -32,6 +33,16 @@ class FusedImagePlan:
         if self.decoder is not None:
             return False
         self.decoder, self.out_h, self.out_w, self.resize = op, int(out_h), int(out_w), bool(resize)
+        return True
+
+    def set_post_crop(self, op, size):
+        """A random-resized-crop transform right behind a pass-through decoder is the crop-and-resize
+        of the decoder itself."""
+        if self.decoder is None or self.resize or self.ops or self.sealed or self.torch_image:
+            return False
+        self.crop_sampler = op
+        self.out_h = self.out_w = int(size)
+        self.resize = True
         return True
 
     def add_spatial(self, native_type, arg, fill, op):
@@ -126,7 +137,7 @@ class FusedImageExecutor:
         n = len(batch_indices)
         params = np.zeros((n, self.n_params), dtype=np.int32)
         crops = np.zeros((n, 4), dtype=np.int32)
-        p.decoder.sample_crops(batch_seed(self.base_seed, epoch, batch_ix, 0), heights, widths, crops)
+        (p.crop_sampler or p.decoder).sample_crops(batch_seed(self.base_seed, epoch, batch_ix, 0), heights, widths, crops)
         params[:, :4] = crops
         for k, (_, _, _, op) in enumerate(p.ops):
             col = np.zeros((n, 2), dtype=np.int32)

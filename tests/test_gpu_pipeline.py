@@ -151,6 +151,34 @@ def test_uint8_output_and_unfused_tail(datasets):
     assert (np.where(is_fill[..., None], expect, g) == expect).all()
 
 
+def test_random_resized_crop_transform(datasets):
+    """The post-decode RandomResizedCrop: folded into the decoder's launch, and on its own."""
+    from ffcv_b200.fields.decoders import SimpleRGBImageDecoder
+    from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, RandomResizedCrop, ToTorchImage
+    pipes = {'image': [SimpleRGBImageDecoder(), RandomResizedCrop((0.3, 1.0), (0.75, 4 / 3), 24), RandomHorizontalFlip(),
+                       NormalizeImage(CIFAR_MEAN, CIFAR_STD, np.float16), ToTorchImage()], 'label': None}
+    loader = _loader(datasets[0], 256, pipes)
+    exe = image_executor(loader)
+    assert exe.plan.resize and exe.plan.out_h == 24 and len(exe.plan.ops) == 1
+    assert next(iter(loader))[0].shape == (256, 3, 24, 24)
+    compare_epoch(loader, max_batches=3)
+    # standalone (behind a torch module): same kernel on the decoded batch
+    from parity import O
+    pipes = {'image': [SimpleRGBImageDecoder(), ch.nn.Identity(), RandomResizedCrop((0.3, 1.0), (0.75, 4 / 3), 20)],
+             'label': None}
+    loader = _loader(datasets[0], 64, pipes)
+    rrc = loader.graph.pipelines[0].ops[2]
+    boxes = []
+    orig = rrc.sample_crops
+    rrc.sample_crops = lambda seed, h, w, out: (orig(seed, h, w, out), boxes.append(out.copy()))[0]
+    got = next(iter(loader))[0].cpu().numpy()
+    raw = next(iter(_loader(datasets[0], 64, {'image': [SimpleRGBImageDecoder()], 'label': None})))[0].cpu().numpy()
+    assert got.shape == (64, 20, 20, 3)
+    for i in range(64):
+        r, c, h, w = (int(v) for v in boxes[0][i])
+        assert np.array_equal(got[i], O.resize_area(raw[i], r, r + h, c, c + w, 20, 20))
+
+
 def test_simple_decoder_rejects_variable_sizes(datasets):
     from ffcv_b200.fields.decoders import SimpleRGBImageDecoder
     with pytest.raises(TypeError):

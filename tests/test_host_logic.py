@@ -191,6 +191,11 @@ def test_fusion_pass_folds_the_reference_pipelines():
     assert k == 2
     plan, k = fuse([RandomResizedCropRGBImageDecoder((64, 64)), ModuleWrapper(ch.nn.Identity()), Cutout(8)])
     assert k == 1 and plan.out_kind == L.OUT_U8_NHWC
+    from ffcv_b200.transforms import RandomResizedCrop
+    plan, k = fuse([dec, RandomResizedCrop((0.08, 1), (0.75, 4 / 3), 24), RandomHorizontalFlip()])
+    assert k == 3 and plan.resize and plan.out_h == 24 and plan.crop_sampler is not None
+    plan, k = fuse([dec, RandomHorizontalFlip(), RandomResizedCrop((0.08, 1), (0.75, 4 / 3), 24)])
+    assert k == 2  # a crop after another augmentation is not the decoder's crop
     plan, k = fuse([RandomResizedCropRGBImageDecoder((64, 64)), Convert(ch.float32)])
     assert k == 2 and plan.table[200, 1] == 200.0
 
