@@ -37,6 +37,15 @@ CFG = 2
 EPOCH_SAMPLES = 200_000
 IMAGENET_MEAN = np.array([0.485, 0.456, 0.406]) * 255
 IMAGENET_STD = np.array([0.229, 0.224, 0.225]) * 255
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per unit of work, from the ncu capture
+# summarised in profiles/config2_batch512_all_kernels.txt (same workload, 512-sample launches):
+# per JPEG sample for the three decode kernels, per sample for the fused resize kernel.
+NCU_DRAM_BYTES_PER_UNIT = {
+    'entropy_decode': (132.45e6 + 132.74e6) / 240,
+    'idct': (133.39e6 + 37.79e6) / 240,
+    'upsample_colour': (42.55e6 + 16.13e6) / 240,
+    'resize_augment_normalise': (137.33e6 + 109.50e6) / 512,
+}
 
 
 def parse_args():
@@ -340,7 +349,9 @@ def main_ours(args):
     algo = {
         'entropy_decode': mean['scan_bytes'] + 128 * mean['blocks'],
         'idct': 128 * mean['blocks'] + mean['plane_bytes'],
-        'upsample_colour': mean['plane_bytes'] + mean['rgb_bytes'],
+        # only the crop box of the JPEG samples is converted: Y + 2 quarter-size chroma planes read
+        # (1.5 B/pixel), RGB written (3 B/pixel); crop_mean is the mean crop size in RGB bytes
+        'upsample_colour': crop_mean * (1.0 - raw_frac) * 1.5,
         'resize_augment_normalise': crop_mean + out_bytes,
     }
     names = list(algo)
@@ -351,8 +362,13 @@ def main_ours(args):
     dom = max(names, key=lambda n: kernels[n]['ms'])
     peak, peak_kind = read_peaks()
     path_bytes = mean['jpeg_bytes'] + crop_mean * raw_frac + out_bytes  # payload read once + output written once
+    units = {'entropy_decode': mean['n_jpeg'], 'idct': mean['n_jpeg'], 'upsample_colour': mean['n_jpeg'],
+             'resize_augment_normalise': float(BATCH)}
+    for n in names:
+        kernels[n]['ncu_dram_bytes'] = NCU_DRAM_BYTES_PER_UNIT[n] * units[n]
     roofline = {'bound': 'hbm', 'kernel': dom, 'achieved': kernels[dom]['gbs'], 'peak': peak, 'unit': 'GB/s',
-                'frac': kernels[dom]['gbs'] / peak, 'traffic': None, 'peak_kind': peak_kind,
+                'frac': kernels[dom]['gbs'] / peak, 'traffic': kernels[dom]['ncu_dram_bytes'], 'peak_kind': peak_kind,
+                'traffic_source': 'ncu capture of the same workload, scaled by the JPEG samples per launch',
                 'ms_per_launch': kernels[dom]['ms'], 'kernels': kernels,
                 'path': {'algorithmic_bytes_per_step': path_bytes, 'kernel_ms_per_step': total_kernel_ms,
                          'gbs': path_bytes / (total_kernel_ms * 1e-3) / 1e9}}
