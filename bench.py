@@ -10,7 +10,9 @@ through RandomResizedCropRGBImageDecoder((224, 224)) -> RandomHorizontalFlip -> 
 seeded sample of that configuration (see --images) written before the timed region.
 
 One JSON line on stdout (rank 0):
-  value      images/s with the batch bytes already resident in HBM (kernels only, CUDA events)
+  value      images/s with the batch bytes already resident in HBM (kernels only, CUDA events), the
+             slots on their own streams as the loader runs them; value_single_stream = the same on
+             one stream (the pass the per-kernel durations come from)
   e2e        images/s through `for batch in Loader(...)`: host staging from the memory-mapped file,
              host->device copy, kernels, and an 8-byte device->host read per step
   roofline   the dominant kernel's algorithmic bytes / its measured duration vs the measured HBM peak
@@ -310,31 +312,53 @@ def main_ours(args):
         p = exe.last_params
         crop_bytes.append(int((p[:, 2].astype(np.int64) * p[:, 3] * 3).sum()))
     ch.cuda.synchronize()
+    # (1) per-kernel durations: one stream, kernels back to back, library events around each
     ctx.set_profiling(True)
     for k in range(args.warmup):
         ctx.rerun(k % slots, stream.cuda_stream, outs[k % slots].data_ptr())
     ch.cuda.synchronize()
     barrier()
     kernel_ms = []
-    v0, v1 = ch.cuda.Event(enable_timing=True), ch.cuda.Event(enable_timing=True)
-    v0.record(stream)
+    s0, s1 = ch.cuda.Event(enable_timing=True), ch.cuda.Event(enable_timing=True)
+    s0.record(stream)
     for k in range(args.steps):
         s = k % slots
         if k >= slots:
             kernel_ms.append(ctx.batch_times(s))  # waits only for a run queued `slots` steps ago
         ctx.rerun(s, stream.cuda_stream, outs[s].data_ptr())
-    v1.record(stream)
+    s1.record(stream)
     ch.cuda.synchronize()
     barrier()
     for s in range(min(slots, args.steps)):
         kernel_ms.append(ctx.batch_times(s))
+    serial_ms = s0.elapsed_time(s1)
+    ctx.set_profiling(False)
+    # (2) throughput the way the loader drives the device: every slot on its own stream, so the
+    # kernels of consecutive batches overlap (the entropy kernel is latency-bound at this batch
+    # size and leaves issue slots to the others)
+    slot_streams = loader.slot_streams()
+    for k in range(args.warmup):
+        ctx.rerun(k % slots, slot_streams[k % slots].cuda_stream, outs[k % slots].data_ptr())
+    ch.cuda.synchronize()
+    barrier()
+    v0, v1 = ch.cuda.Event(enable_timing=True), ch.cuda.Event(enable_timing=True)
+    v0.record(stream)
+    for st_ in slot_streams:
+        st_.wait_event(v0)
+    for k in range(args.steps):
+        ctx.rerun(k % slots, slot_streams[k % slots].cuda_stream, outs[k % slots].data_ptr())
+    for st_ in slot_streams:
+        stream.wait_stream(st_)
+    v1.record(stream)
+    ch.cuda.synchronize()
+    barrier()
     value_ms = v0.elapsed_time(v1)
     clocks = sampler.stop() if rank == 0 else None
 
-    times = ch.tensor([e2e_ms, value_ms, staged_ms], dtype=ch.float64, device=device)
+    times = ch.tensor([e2e_ms, value_ms, staged_ms, serial_ms], dtype=ch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    e2e_ms, value_ms, staged_ms = (float(v) for v in times.cpu())
+    e2e_ms, value_ms, staged_ms, serial_ms = (float(v) for v in times.cpu())
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -397,6 +421,8 @@ def main_ours(args):
             'e2e_pinned_file': {'value': BATCH * world * args.steps / (staged_ms * 1e-3), 'unit': 'images/s',
                                 'ms_per_step': staged_ms / args.steps, 'h2d_bytes_per_step': staged_h2d,
                                 'source': 'Loader(pin_file=True): file in pinned host RAM, payloads gathered by the GPU'},
+            'value_single_stream': {'value': BATCH * world * args.steps / (serial_ms * 1e-3), 'unit': 'images/s',
+                                    'ms_per_step': serial_ms / args.steps},
             'gpu_launches': int(launches_per_batch * args.steps), 'roofline': roofline, 'cpu_baseline': cpu,
             'clocks': clocks, 'digest': digest}
     print(json.dumps(line, default=float))
