@@ -42,24 +42,44 @@ class Pool {
     }
     // Runs fn(i) for i in [0, n) on the pool and the calling thread; returns when all are done.
     void parallel_for(int n, const std::function<void(int)> &fn) {
+        start(n, fn);
+        wait();
+    }
+    // Hands fn(i), i in [0, n), to the pool threads and returns; wait() (which also lends the
+    // calling thread) must be called before the next start().
+    void start(int n, std::function<void(int)> fn) {
+        wait();
         if (n <= 0) return;
-        if (workers_.empty() || n == 1) {
-            for (int i = 0; i < n; i++) fn(i);
-            return;
+        job_ = std::move(fn);
+        if (workers_.empty()) {
+            n_ = n;
+            next_.store(0);
+            busy_ = true;
+            return; // wait() runs it
         }
         {
             std::lock_guard<std::mutex> g(m_);
-            fn_ = &fn;
+            fn_ = &job_;
             n_ = n;
             next_.store(0);
             pending_ = (int)workers_.size();
             generation_++;
         }
+        busy_ = true;
         cv_.notify_all();
-        drain();
-        std::unique_lock<std::mutex> g(m_);
-        done_cv_.wait(g, [this] { return pending_ == 0; });
+    }
+    void wait() {
+        if (!busy_) return;
+        if (workers_.empty()) {
+            fn_ = &job_;
+            drain();
+        } else {
+            drain();
+            std::unique_lock<std::mutex> g(m_);
+            done_cv_.wait(g, [this] { return pending_ == 0; });
+        }
         fn_ = nullptr;
+        busy_ = false;
     }
     int size() const { return (int)workers_.size() + 1; }
 
@@ -94,6 +114,8 @@ class Pool {
     uint64_t generation_;
     int pending_;
     const std::function<void(int)> *fn_ = nullptr;
+    std::function<void(int)> job_;
+    bool busy_ = false; // touched by the owning (calling) thread only
     int n_ = 0;
     std::atomic<int> next_{0};
 };
@@ -120,7 +142,6 @@ void stream_copy(uint8_t *dst, const uint8_t *src, size_t n) {
         _mm_stream_si128(reinterpret_cast<__m128i *>(dst + k + 48), d);
     }
     if (k < n) memcpy(dst + k, src + k, n - k);
-    _mm_sfence();
 }
 
 struct DevBuf {
@@ -141,6 +162,9 @@ struct Slot {
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes = 0, raw_bytes = 0, jpeg_bytes = 0;
     bool staged = false;
     bool direct = false; // payloads are gathered by the GPU from pinned host memory
+    bool copying = false; // the payload copy of the staged batch may still be running on the pool
+    std::vector<ImageDesc> descs;
+    std::vector<uint64_t> src_ptrs;
     double stage_ms[4] = {0, 0, 0, 0}; // header parse, layout, payload copy, total
     std::vector<JpegHeader> headers;
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -169,6 +193,7 @@ struct ffcvb_ctx {
     AuxBuf aux[4];
     int aux_next = 0;
     bool profile = false;
+    bool async_staging = false;
     DevBuf one_src, one_dst; // single-image entry points
 };
 
@@ -279,6 +304,7 @@ int ffcvb_create(int device, int n_slots, int n_threads, ffcvb_ctx **out) {
 
 void ffcvb_destroy(ffcvb_ctx *ctx) {
     if (!ctx) return;
+    ctx->pool->wait();
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
     for (auto &s : ctx->slots) {
@@ -333,7 +359,11 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     }
     const bool direct = src_dev_base != 0;
     s.direct = direct;
-    std::vector<ImageDesc> descs(n);
+    ctx->pool->wait(); // a previous batch's copy may still use the pool
+    for (auto &o : ctx->slots) o.copying = false;
+    std::vector<ImageDesc> &descs = s.descs;
+    descs.assign(n, ImageDesc{});
+    s.src_ptrs.assign(ptrs, ptrs + n);
     s.headers.resize(n);
 
     // ---- per-sample: parse headers, decide what to stage
@@ -385,7 +415,8 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
             d.rows = (uint16_t)rows;
             d.col0 = (uint16_t)c0;
             d.cols = (uint16_t)cols;
-            d.payload_size = (uint32_t)((size_t)rows * cols * 3);
+            d.raw_pitch = (uint32_t)cols * 3;
+            d.payload_size = (uint32_t)((size_t)rows * d.raw_pitch);
             if (direct && rows > 0) d.src_addr = src_dev_base + ptrs[i] + (uint64_t)r0 * d.width * 3;
         }
         if (direct && modes[i] == FFCVB_MODE_JPG) d.src_addr = src_dev_base + ptrs[i];
@@ -516,22 +547,31 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     const auto t2 = std::chrono::steady_clock::now();
     // ---- parallel: gather the payload bytes into pinned memory
     uint8_t *host = s.host;
-    if (!direct) ctx->pool->parallel_for(n, [&](int i) {
-        const ImageDesc &d = descs[i];
-        if (d.payload_size == 0) return;
-        const uint8_t *src = file_base + ptrs[i];
-        uint8_t *dst = host + d.payload_off;
-        if (d.mode == FFCVB_MODE_RAW && d.cols != d.width) {
-            // only the crop box travels: one run per row
-            const size_t pitch = (size_t)d.width * 3, run = (size_t)d.cols * 3;
-            src += (size_t)d.row0 * pitch + (size_t)d.col0 * 3;
-            for (int r = 0; r < d.rows; r++) memcpy(dst + r * run, src + r * pitch, run);
-        } else {
-            if (d.mode == FFCVB_MODE_RAW) src += (size_t)d.row0 * d.width * 3;
-            stream_copy(dst, src, d.payload_size);
+    if (!direct) {
+        Slot *sp = &s; // the job may outlive this call: it only touches slot-owned data and the source
+        ctx->pool->start(n, [sp, host, file_base](int i) {
+            const ImageDesc &d = sp->descs[i];
+            if (d.payload_size == 0) return;
+            const uint8_t *src = file_base + sp->src_ptrs[i];
+            uint8_t *dst = host + d.payload_off;
+            if (d.mode == FFCVB_MODE_RAW && d.cols != d.width) {
+                // only the crop box travels: one run per row.  Plain copies: streaming stores on
+                // ~1 KB rows leave partial write-combining lines and measured almost twice slower
+                const size_t pitch = (size_t)d.width * 3, run = (size_t)d.cols * 3;
+                src += (size_t)d.row0 * pitch + (size_t)d.col0 * 3;
+                for (int r = 0; r < d.rows; r++) memcpy(dst + r * (size_t)d.raw_pitch, src + r * pitch, run);
+            } else {
+                if (d.mode == FFCVB_MODE_RAW) src += (size_t)d.row0 * d.width * 3;
+                stream_copy(dst, src, d.payload_size);
+            }
+            _mm_sfence(); // streaming stores are weakly ordered: publish them before the batch is submitted
+        });
+        s.copying = true;
+        if (!ctx->async_staging) {
+            ctx->pool->wait();
+            s.copying = false;
         }
-    });
-
+    }
     const auto t3 = std::chrono::steady_clock::now();
     auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
     s.stage_ms[0] = ms(t0, t1);
@@ -636,6 +676,14 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
     return FFCVB_OK;
 }
 
+int ffcvb_set_async_staging(ffcvb_ctx *ctx, int enabled) {
+    if (!ctx) return FFCVB_E_ARG;
+    ctx->pool->wait();
+    for (auto &o : ctx->slots) o.copying = false;
+    ctx->async_staging = enabled != 0;
+    return FFCVB_OK;
+}
+
 int ffcvb_set_profiling(ffcvb_ctx *ctx, int enabled) {
     if (!ctx) return FFCVB_E_ARG;
     ctx->profile = enabled != 0;
@@ -660,6 +708,10 @@ int ffcvb_submit_batch(ffcvb_ctx *ctx, int slot, void *stream, void *out_dev) {
         return fail(ctx, FFCVB_E_ARG, "ffcvb_submit_batch: bad argument");
     Slot &s = ctx->slots[slot];
     if (!s.staged) return fail(ctx, FFCVB_E_ARG, "ffcvb_submit_batch: slot %d has no staged batch", slot);
+    if (s.copying) { // asynchronous staging: the copy was left running
+        ctx->pool->wait();
+        s.copying = false;
+    }
     CU(cudaSetDevice(ctx->device));
     return run_batch(ctx, s, (cudaStream_t)stream, out_dev, true);
 }

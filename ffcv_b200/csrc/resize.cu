@@ -142,7 +142,7 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
             base = src.blob + d.payload_off;
             row0 = d.row0;
             col0 = d.col0;
-            stride = d.cols * 3;
+            stride = (int)d.raw_pitch;
             ok = d.host_status == 0;
         } else {
             base = src.rgb + d.rgb_off;

@@ -18,7 +18,8 @@ struct ImageDesc {
     int16_t host_status;   // 0, or a negative code when the host parser rejected the stream
     uint16_t height, width;
     uint16_t row0, rows;   // raw: first image row present in the staged payload, number of rows
-    uint16_t col0, cols;   // raw: first image column present, number of columns (row pitch = cols * 3)
+    uint16_t col0, cols;   // raw: first image column present, number of columns
+    uint32_t raw_pitch;    // raw: bytes between staged rows (>= cols * 3)
     // ---- JPEG only ----
     uint32_t scan_off;     // entropy-coded segment, relative to payload_off
     uint32_t scan_len;

@@ -50,6 +50,8 @@ lib.ffcvb_submit_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_submit_batch.restype = c_int
 lib.ffcvb_rerun_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_rerun_batch.restype = c_int
+lib.ffcvb_set_async_staging.argtypes = [c_void_p, c_int]
+lib.ffcvb_set_async_staging.restype = c_int
 lib.ffcvb_set_profiling.argtypes = [c_void_p, c_int]
 lib.ffcvb_set_profiling.restype = c_int
 lib.ffcvb_batch_times.argtypes = [c_void_p, c_int, c_void_p]
@@ -102,6 +104,12 @@ def make_plan(out_h, out_w, resize, out_kind, ops=(), lut_dev=0):
     return plan
 
 
+def _as(a, dtype):
+    if isinstance(a, np.ndarray) and a.dtype == dtype and a.flags.c_contiguous:
+        return a
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
 class FFCVBError(RuntimeError):
     pass
 
@@ -125,12 +133,12 @@ class Context:
 
     def stage(self, slot, file_base, ptrs, sizes, modes, heights, widths, plan, params):
         """file_base: integer address (or uint8 array) the sample pointers are relative to."""
-        ptrs = np.ascontiguousarray(ptrs, dtype=np.uint64)
-        sizes = np.ascontiguousarray(sizes, dtype=np.uint64)
-        modes = np.ascontiguousarray(modes, dtype=np.uint8)
-        heights = np.ascontiguousarray(heights, dtype=np.uint16)
-        widths = np.ascontiguousarray(widths, dtype=np.uint16)
-        params = np.ascontiguousarray(params, dtype=np.int32)
+        ptrs = _as(ptrs, np.uint64)
+        sizes = _as(sizes, np.uint64)
+        modes = _as(modes, np.uint8)
+        heights = _as(heights, np.uint16)
+        widths = _as(widths, np.uint16)
+        params = _as(params, np.int32)
         n = len(ptrs)
         assert params.shape == (n, 4 + 2 * plan.n_ops), params.shape
         base = file_base.ctypes.data if isinstance(file_base, np.ndarray) else int(file_base)
@@ -144,6 +152,9 @@ class Context:
 
     def rerun(self, slot, stream, out_ptr):
         self._check(lib.ffcvb_rerun_batch(self._h, slot, stream or None, out_ptr), 'ffcvb_rerun_batch')
+
+    def set_async_staging(self, enabled):
+        self._check(lib.ffcvb_set_async_staging(self._h, int(bool(enabled))), 'ffcvb_set_async_staging')
 
     def set_profiling(self, enabled):
         self._check(lib.ffcvb_set_profiling(self._h, int(bool(enabled))), 'ffcvb_set_profiling')

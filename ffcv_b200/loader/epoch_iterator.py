@@ -100,8 +100,9 @@ class EpochIterator(Thread):
         with ch.cuda.stream(stream):
             if cuda_event is not None:
                 cuda_event.wait()
+            lookahead = self.batches[b_ix + 1] if b_ix + 1 < len(self.batches) else None
             result = self.loader.graph.run_batch(batch_indices, slot, stream.cuda_stream, self.buffers,
-                                                 self.storage_state, self.epoch, b_ix)
+                                                 self.storage_state, self.epoch, b_ix, lookahead=lookahead)
             done = ch.cuda.Event()
             done.record(stream)
             self.slot_done[slot] = done

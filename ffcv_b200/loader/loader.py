@@ -172,6 +172,8 @@ class Loader:
         if index not in self._contexts:
             self._contexts[index] = L.Context(index, n_slots=self.batches_ahead + 2,
                                               n_threads=self.num_workers)
+            # the payload copy of a batch overlaps the drawing of the next batch's parameters
+            self._contexts[index].set_async_staging(True)
         return self._contexts[index]
 
     def slot_streams(self):

@@ -121,6 +121,7 @@ class FusedImageExecutor:
                                        self.table_dev.data_ptr() if self.table_dev is not None else 0)
         self.n_params = 4 + 2 * len(ops)
         self.last_params = None
+        self._prepared = None     # ((epoch, batch, n), arrays) drawn ahead for the next batch
         self.param_log = None     # set to a list to record (epoch, batch, indices, parameter table) per batch
         self.h2d_bytes = 0
         self.launches = 0
@@ -145,14 +146,30 @@ class FusedImageExecutor:
             params[:, 4 + 2 * k:6 + 2 * k] = col
         return md, heights, widths, params
 
-    def __call__(self, batch_indices, slot, stream_ptr, out, epoch, batch_ix):
+    def prepare(self, batch_indices, epoch, batch_ix):
+        """Everything ffcvb_stage_batch needs for one batch, as contiguous arrays."""
         md, heights, widths, params = self.sample_params(batch_indices, epoch, batch_ix)
+        return (np.ascontiguousarray(md['data_ptr'], dtype=np.uint64),
+                np.ascontiguousarray(self.sample_sizes[batch_indices], dtype=np.uint64),
+                np.ascontiguousarray(md['mode'], dtype=np.uint8), heights, widths, params)
+
+    def __call__(self, batch_indices, slot, stream_ptr, out, epoch, batch_ix, lookahead=None):
+        key = (epoch, batch_ix, len(batch_indices))
+        if self._prepared is not None and self._prepared[0] == key:
+            args = self._prepared[1]
+        else:
+            args = self.prepare(batch_indices, epoch, batch_ix)
+        self._prepared = None
+        params = args[5]
         self.last_params = params
         if self.param_log is not None:
             self.param_log.append((epoch, batch_ix, np.array(batch_indices), params.copy()))
         n = len(batch_indices)
-        self.ctx.stage(slot, self.file_base_fn(), md['data_ptr'], self.sample_sizes[batch_indices],
-                       md['mode'], heights, widths, self.native_plan, params)
+        # with asynchronous staging this returns while the staging threads still copy the payloads ...
+        self.ctx.stage(slot, self.file_base_fn(), *args[:5], self.native_plan, params)
+        # ... which is when the next batch's parameters are drawn
+        if lookahead is not None:
+            self._prepared = ((epoch, batch_ix + 1, len(lookahead)), self.prepare(lookahead, epoch, batch_ix + 1))
         dst = out[:n]
         self.ctx.submit(slot, stream_ptr, dst.data_ptr())
         self.h2d_bytes = self.ctx.staged_bytes(slot)

@@ -145,13 +145,14 @@ class Graph:
             return tuple(Graph._select(b, slot, count) for b in buffer)
         return buffer[slot][:count]
 
-    def run_batch(self, batch_indices, slot, stream_ptr, buffers, storage_state, epoch, batch_ix):
+    def run_batch(self, batch_indices, slot, stream_ptr, buffers, storage_state, epoch, batch_ix, lookahead=None):
         """One batch through every pipeline; returns the outputs in declaration order."""
         n = len(batch_indices)
         results = []
         for pi, p in enumerate(self.pipelines):
             if p.executor is not None:
-                value = p.executor(batch_indices, slot, stream_ptr, buffers[(pi, 'fused')][slot], epoch, batch_ix)
+                value = p.executor(batch_indices, slot, stream_ptr, buffers[(pi, 'fused')][slot], epoch, batch_ix,
+                                   lookahead=lookahead)
                 first = p.n_fused
             else:
                 code = p.codes[0]

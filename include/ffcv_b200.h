@@ -102,6 +102,12 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                       const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
                       const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params);
 
+/* With asynchronous staging enabled, ffcvb_stage_batch returns as soon as the batch is laid out
+ * and leaves the payload copy running on the staging threads; ffcvb_submit_batch of that slot
+ * waits for it.  The caller must keep `file_base` mapped until then and may use the time in
+ * between to prepare the next batch.  Off by default. */
+int ffcvb_set_async_staging(ffcvb_ctx *ctx, int enabled);
+
 /* Queue the staged batch on `stream`: one host->device copy of the staged bytes, then the decode
  * (entropy decode, dequantise + IDCT, chroma upsample + colour conversion) and the fused
  * crop/resize/augment/normalise kernels, writing `n` images into `out_dev` (DEVICE pointer,
