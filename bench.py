@@ -53,8 +53,8 @@ NCU_DRAM_BYTES_PER_UNIT = {
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=40)
-    ap.add_argument('--warmup', type=int, default=8)
+    ap.add_argument('--steps', type=int, default=200)
+    ap.add_argument('--warmup', type=int, default=10)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--images', type=int, default=4096, help='distinct images in the synthetic dataset')
     ap.add_argument('--workers', type=int, default=0, help='host staging threads per rank (0: cores / ranks)')
@@ -110,7 +110,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits',
-                                          '-lms', '200', '-i', str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          '-lms', '100', '-i', str(self.index)], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:

@@ -12,9 +12,11 @@
  * reference's ffcv-conda.yml), which is not vendored in the reference tree; this file is written
  * from the JPEG standard (ITU-T T.81), the published AAN and Loeffler-Ligtenberg-Moschytz IDCT
  * factorisations, and from behaviour observed through the libjpeg-turbo binaries bundled with
- * Pillow (fast IDCT + replicated chroma, "draft" decoder config) and OpenCV (accurate IDCT + fancy
- * upsampling).  Both of those binaries pin this file in tests/test_oracle_jpeg.py; the accurate
- * IDCT and the replicated upsampler exist here only so that each stage can be pinned that way.
+ * Pillow and OpenCV.  Pinned (tests/test_oracle_golden.py, tests/test_oracle_live.py) bit for bit
+ * on (a) Pillow's libjpeg-turbo driven through the libjpeg API with the fast integer IDCT and fancy
+ * upsampling -- the reference's configuration itself; (b) Pillow's "draft" decoder configuration
+ * (fast IDCT + replicated chroma); (c) cv2.imdecode (accurate IDCT + fancy upsampling).  The
+ * accurate IDCT and the replicated upsampler exist here only for (b) and (c).
  *
  * Supported streams: 8-bit baseline/extended-sequential Huffman (SOF0/SOF1), one interleaved scan,
  * 1 or 3 components, luma sampling 1x1, 2x1 or 2x2 with 1x1 chroma, optional restart intervals.

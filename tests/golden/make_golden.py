@@ -3,11 +3,13 @@
     python tests/golden/make_golden.py
 
 jpeg_cases.npz    JPEG streams written by cv2.imencode (the call the reference's writer makes,
-                  ffcv/fields/rgb_image.py:26-34) with their pixels as decoded by two libjpeg-turbo
-                  binaries: Pillow with decoder config (scale 1, draft 1) = fast integer IDCT +
-                  replicated chroma, and cv2.imdecode = accurate IDCT + triangle ("fancy")
-                  upsampling.  Together they pin every stage of the reference's TurboJPEG call
-                  (fast IDCT + fancy upsampling), which no Python binding here can select directly.
+                  ffcv/fields/rgb_image.py:26-34) with their pixels as decoded by real libjpeg-turbo
+                  binaries: `turbo_fast_fancy_*` = Pillow's bundled libjpeg-turbo driven through
+                  the libjpeg API with dct_method = JDCT_IFAST and fancy upsampling on, i.e. the
+                  configuration of the reference's TurboJPEG call (tests/libjpeg_direct.py);
+                  `fast_replicate_*` = Pillow with decoder config (scale 1, draft 1) = fast integer
+                  IDCT + replicated chroma; `accurate_fancy_*` = cv2.imdecode = accurate IDCT +
+                  triangle ("fancy") upsampling.
 resize_cases.npz  inputs and outputs of cv2.resize(INTER_AREA), the call of libffcv.cpp:40-41.
 crop_cases.npz    crop boxes from the reference's own get_random_crop / get_center_crop
                   (function source taken from /root/reference/ffcv/fields/rgb_image.py at
@@ -19,9 +21,14 @@ import ast
 import io
 import os
 
+import sys
+
 import cv2
 import numpy as np
 from PIL import Image
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import libjpeg_direct  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF = '/root/reference/ffcv/fields/rgb_image.py'
@@ -76,6 +83,7 @@ def jpeg_cases():
         out[f'jpeg_{k}'] = buf
         out[f'fast_replicate_{k}'] = pil_draft(buf)
         out[f'accurate_fancy_{k}'] = np.ascontiguousarray(cv2.imdecode(buf, cv2.IMREAD_COLOR)[..., ::-1])
+        out[f'turbo_fast_fancy_{k}'] = libjpeg_direct.decode(buf, libjpeg_direct.JDCT_IFAST, True)
     out['count'] = np.array(len(specs))
     np.savez_compressed(os.path.join(HERE, 'jpeg_cases.npz'), **out)
 

@@ -16,6 +16,8 @@ def test_jpeg_decode_stages_against_libjpeg_turbo_vectors():
     assert n >= 10
     for k in range(n):
         buf = z[f'jpeg_{k}']
+        # the reference's configuration itself: fast integer IDCT + fancy upsampling
+        assert np.array_equal(O.jpeg_decode(buf), z[f'turbo_fast_fancy_{k}']), k
         # entropy decode + dequantisation + fast integer IDCT + colour conversion
         a = O.jpeg_decode(buf, O.IDCT_FAST, O.UPSAMPLE_REPLICATE)
         assert np.array_equal(a, z[f'fast_replicate_{k}']), k

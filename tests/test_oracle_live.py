@@ -55,6 +55,32 @@ def test_jpeg_random_streams():
         assert np.array_equal(O.jpeg_decode(buf, O.IDCT_ACCURATE, O.UPSAMPLE_FANCY), want), t
 
 
+def test_reference_configuration_against_libjpeg_turbo_directly():
+    """Fast integer IDCT + fancy upsampling, the TurboJPEG configuration of libffcv.cpp:104-106,
+    decoded by the libjpeg-turbo binary bundled with Pillow (see tests/libjpeg_direct.py)."""
+    import libjpeg_direct as T
+    from ffcv_b200.synthetic import synth_content
+    if not T.available():
+        pytest.skip('no bundled libjpeg-turbo to drive')
+    rng = np.random.default_rng(9)
+    cases = [(64, 64, 90, 420, 'smooth'), (385, 390, 90, 420, 'smooth'), (37, 53, 75, 420, 'noise'),
+             (200, 250, 100, 420, 'noise'), (500, 333, 90, 420, 'smooth'), (17, 9, 90, 420, 'noise'),
+             (300, 301, 95, 444, 'smooth'), (120, 90, 100, 444, 'binary'), (101, 100, 90, 422, 'smooth'),
+             (8, 8, 50, 420, 'noise'), (256, 192, 30, 420, 'smooth'), (96, 160, 5, 420, 'noise')]
+    for h, w, q, samp, kind in cases:
+        if kind == 'noise':
+            img = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+        elif kind == 'binary':
+            img = (rng.integers(0, 2, (h, w, 3)) * 255).astype(np.uint8)
+        else:
+            img = synth_content(rng, h, w)
+        buf = _encode(img, q, samp)
+        assert np.array_equal(O.jpeg_decode(buf), T.decode(buf, T.JDCT_IFAST, True)), (h, w, q, samp)
+        # the harness itself: library defaults reproduce cv2's decoder
+        want = cv2.imdecode(buf, cv2.IMREAD_COLOR)[..., ::-1]
+        assert np.array_equal(T.decode(buf, T.JDCT_ISLOW, True), want), (h, w, q, samp)
+
+
 def test_jpeg_benchmark_shaped_images():
     from ffcv_b200.synthetic import synth_content
     rng = np.random.default_rng(2)
