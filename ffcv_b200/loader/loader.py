@@ -2,6 +2,7 @@
 iteration protocol; batches are decoded and augmented on the GPU of the calling process."""
 import enum
 from os import environ, sched_getaffinity
+from os.path import getsize
 from typing import Any, Callable, Mapping, Sequence, Type, Union
 
 import numpy as np
@@ -75,7 +76,12 @@ class Loader:
         fetch each batch's bytes itself over PCIe instead of staging them with CPU threads: no
         host core touches sample bytes, at the price of some GPU throughput (the gather shares
         the memory system with the decode kernels) and of one pinned copy of the file per
-        process.  Default off; ``FFCV_B200_PIN_FILE=1`` turns it on.
+        process.  Default (``None``): on when this rank has fewer than 12 staging threads
+        (``num_workers``, or its share of the node's cores) and the file is at most
+        ``FFCV_B200_PIN_LIMIT_GB`` (default 64) GiB -- with few host cores per GPU the CPU copy is
+        the bottleneck (8 GPUs on 32 cores: 819 k img/s gathered vs 342 k staged), with many it is
+        the faster path (1 GPU on 16 cores: 232 k staged vs 172 k gathered).  ``FFCV_B200_PIN_FILE``
+        = 0 / 1 overrides.
     """
 
     def __init__(self, fname: str, batch_size: int, num_workers: int = -1,
@@ -116,8 +122,13 @@ class Loader:
         else:
             self.indices = np.array(indices)
 
+        if pin_file is None and environ.get('FFCV_B200_PIN_FILE') in ('0', '1'):
+            pin_file = environ['FFCV_B200_PIN_FILE'] == '1'
         if pin_file is None:
-            pin_file = environ.get('FFCV_B200_PIN_FILE', '0') == '1'
+            threads = num_workers if num_workers >= 1 else \
+                len(sched_getaffinity(0)) // max(1, int(environ.get('LOCAL_WORLD_SIZE', '1')))
+            limit = float(environ.get('FFCV_B200_PIN_LIMIT_GB', '64')) * (1 << 30)
+            pin_file = ch.cuda.is_available() and threads < 12 and getsize(fname) <= limit
         self.pin_file = bool(pin_file)
         self.memory_manager: MemoryManager = OSCacheManager(self.reader, pin=self.pin_file)
 
