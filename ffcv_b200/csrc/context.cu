@@ -400,10 +400,8 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                     p[1] + p[3] <= (int)d.width) {
                     r0 = p[0];
                     rows = p[2];
-                    if (!direct) { // the CPU copies just the crop box; the GPU gather takes whole rows
-                        c0 = p[1];
-                        cols = p[3];
-                    }
+                    c0 = p[1];
+                    cols = p[3];
                 }
             }
             const uint64_t need = (uint64_t)d.height * d.width * 3;
@@ -417,7 +415,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
             d.cols = (uint16_t)cols;
             d.raw_pitch = (uint32_t)cols * 3;
             d.payload_size = (uint32_t)((size_t)rows * d.raw_pitch);
-            if (direct && rows > 0) d.src_addr = src_dev_base + ptrs[i] + (uint64_t)r0 * d.width * 3;
+            if (direct && rows > 0) d.src_addr = src_dev_base + ptrs[i] + ((uint64_t)r0 * d.width + c0) * 3;
         }
         if (direct && modes[i] == FFCVB_MODE_JPG) d.src_addr = src_dev_base + ptrs[i];
     });
@@ -519,7 +517,8 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     hd.payload_off = off;
     for (int i = 0; i < n; i++) {
         // gathered payloads keep their source alignment mod 16 so both sides move in 16-byte words
-        descs[i].payload_off = off + (direct ? (descs[i].src_addr & 15) : 0);
+        const bool rowwise = descs[i].mode == FFCVB_MODE_RAW && descs[i].cols != descs[i].width;
+        descs[i].payload_off = off + ((direct && !rowwise) ? (descs[i].src_addr & 15) : 0);
         off = align_up(descs[i].payload_off + descs[i].payload_size, kPayloadAlign);
     }
     hd.total_bytes = off;

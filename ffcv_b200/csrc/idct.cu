@@ -148,11 +148,47 @@ __device__ __forceinline__ int chroma_sample(const uint8_t *__restrict__ p, int 
 // system for the decode kernels running beside it (48 x 512 threads halved a concurrent HBM copy).
 __global__ void __launch_bounds__(256)
 gather_payloads_kernel(const ImageDesc *__restrict__ descs, int n, uint8_t *__restrict__ blob) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     for (int i = blockIdx.x; i < n; i += gridDim.x) {
         const ImageDesc &d = descs[i];
         if (d.src_addr == 0 || d.payload_size == 0) continue;
         const uint8_t *src = reinterpret_cast<const uint8_t *>(d.src_addr);
         uint8_t *dst = blob + d.payload_off;
+        if (d.mode == 1 && d.cols != d.width) {
+            // Raw sample, crop box only: one warp per row.  The row's bytes are fetched as the
+            // 16-byte chunks of host memory that contain them (all of a row's requests are issued
+            // before the first store) and land tightly packed in the blob.
+            const uint32_t run = (uint32_t)d.cols * 3, pitch = (uint32_t)d.width * 3;
+            for (int r = warp; r < d.rows; r += nwarps) {
+                const uint8_t *s = src + (size_t)r * pitch;
+                uint8_t *o = dst + (size_t)r * d.raw_pitch;
+                const uint32_t a = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
+                const uint4 *s16 = reinterpret_cast<const uint4 *>(s - a);
+                const uint32_t nchunk = (a + run + 15) >> 4;
+                uint4 v[4];
+#pragma unroll 1
+                for (uint32_t c0 = 0; c0 < nchunk; c0 += 128) {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const uint32_t c = c0 + u * 32 + lane;
+                        if (c < nchunk) v[u] = s16[c];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const uint32_t c = c0 + u * 32 + lane;
+                        if (c >= nchunk) continue;
+                        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                        const int base = (int)(c << 4) - (int)a;
+#pragma unroll
+                        for (int b = 0; b < 16; b++) {
+                            const int k = base + b;
+                            if (k >= 0 && k < (int)run) o[k] = (uint8_t)(w[b >> 2] >> (8 * (b & 3)));
+                        }
+                    }
+                }
+            }
+            continue;
+        }
         const uint32_t size = d.payload_size;
         uint32_t head = (uint32_t)((16 - (d.src_addr & 15)) & 15);
         if (head > size) head = size;
