@@ -289,7 +289,7 @@ def main_ours(args):
 
     # ------------------------------------------------------------------ end to end (public API)
     # Both ways the bytes can reach the GPU are timed; `e2e` is the one Loader picks by itself for
-    # this host (pin_file=None: GPU gather when a rank has fewer than 12 staging threads).
+    # this host (pin_file=None: GPU gather when a rank has fewer than 16 staging threads).
     auto_pin = make_loader(None).memory_manager.pin
     other = make_loader(not auto_pin)
     other_ms, other_h2d, _, _ = run_e2e(other)
@@ -402,6 +402,20 @@ def main_ours(args):
                 'path': {'algorithmic_bytes_per_step': path_bytes, 'kernel_ms_per_step': total_kernel_ms,
                          'gbs': path_bytes / (total_kernel_ms * 1e-3) / 1e9}}
 
+    # host->device link: the binding roofline of the end-to-end rate (pinned copy, 256 MB, best of 5)
+    hbuf = ch.empty(256 << 20, dtype=ch.uint8).pin_memory()
+    dbuf = ch.empty(256 << 20, dtype=ch.uint8, device=device)
+    best = 1e9
+    for _ in range(6):
+        a, b = ch.cuda.Event(enable_timing=True), ch.cuda.Event(enable_timing=True)
+        a.record()
+        dbuf.copy_(hbuf, non_blocking=True)
+        b.record()
+        b.synchronize()
+        best = min(best, a.elapsed_time(b))
+    h2d_peak = (256 << 20) / (best * 1e-3) / 1e9
+    del hbuf, dbuf
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         threads = cores
@@ -421,6 +435,9 @@ def main_ours(args):
             'e2e': {'value': BATCH * world * args.steps / (e2e_ms * 1e-3), 'unit': 'images/s',
                     'ms_per_step': e2e_ms / args.steps, 'h2d_bytes_per_step': h2d_mean,
                     'd2h_bytes_per_step': 8,
+                    'h2d_roofline': {'bound': 'host->device link', 'achieved': h2d_mean / (e2e_ms / args.steps * 1e-3) / 1e9,
+                                     'peak': h2d_peak, 'unit': 'GB/s', 'frac': h2d_mean / (e2e_ms / args.steps * 1e-3) / 1e9 / h2d_peak,
+                                     'note': 'per GPU, rank 0; peak = pinned 256 MB cudaMemcpy measured in this run'},
                     'source': 'file pinned in host RAM, payloads gathered by the GPU over PCIe' if loader.memory_manager.pinned
                     else 'file memory-mapped, staged by CPU threads'},
             'e2e_staged': {'value': BATCH * world * args.steps / (staged_ms * 1e-3), 'unit': 'images/s',

@@ -76,11 +76,12 @@ class Loader:
         fetch each batch's bytes itself over PCIe instead of staging them with CPU threads: no
         host core touches sample bytes, at the price of some GPU throughput (the gather shares
         the memory system with the decode kernels) and of one pinned copy of the file per
-        process.  Default (``None``): on when this rank has fewer than 12 staging threads
+        process.  Default (``None``): on when this rank has fewer than 16 staging threads
         (``num_workers``, or its share of the node's cores) and the file is at most
         ``FFCV_B200_PIN_LIMIT_GB`` (default 64) GiB -- with few host cores per GPU the CPU copy is
-        the bottleneck (8 GPUs on 32 cores: 819 k img/s gathered vs 342 k staged), with many it is
-        the faster path (1 GPU on 16 cores: 232 k staged vs 172 k gathered).  ``FFCV_B200_PIN_FILE``
+        the bottleneck (8 GPUs on 32 cores: 819 k img/s gathered vs 342 k staged; 1 GPU with 4
+        threads: 243 k vs 118 k), with 16 both run at the PCIe rate (~250 k img/s) and staging
+        avoids pinning the file.  ``FFCV_B200_PIN_FILE``
         = 0 / 1 overrides.
     """
 
@@ -128,7 +129,7 @@ class Loader:
             threads = num_workers if num_workers >= 1 else \
                 len(sched_getaffinity(0)) // max(1, int(environ.get('LOCAL_WORLD_SIZE', '1')))
             limit = float(environ.get('FFCV_B200_PIN_LIMIT_GB', '64')) * (1 << 30)
-            pin_file = ch.cuda.is_available() and threads < 12 and getsize(fname) <= limit
+            pin_file = ch.cuda.is_available() and threads < 16 and getsize(fname) <= limit
         self.pin_file = bool(pin_file)
         self.memory_manager: MemoryManager = OSCacheManager(self.reader, pin=self.pin_file)
 
