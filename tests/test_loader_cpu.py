@@ -1,0 +1,155 @@
+"""Loader behaviour that needs no GPU: pipelines over the label field only (the image field is
+disabled with `None`, as the reference allows), so everything runs on the host.  Mirrors the
+reference's plumbing tests (tests/test_partial_batches.py, test_partial_pipeline.py,
+test_loader_filter.py, test_basic_pipeline.py)."""
+from dataclasses import replace
+
+import numpy as np
+import pytest
+import torch as ch
+
+
+@pytest.fixture(scope='module')
+def beton(tmp_path_factory):
+    from ffcv_b200.synthetic import write_dataset
+    d = tmp_path_factory.mktemp('loadercpu')
+    return write_dataset(0, str(d / 'c0.beton'), 203, num_workers=1)
+
+
+def _labels(path):
+    from ffcv_b200.reader import Reader
+    return Reader(path).metadata['f1'].copy()
+
+
+def _loader(path, **kw):
+    from ffcv_b200 import Loader
+    from ffcv_b200.fields.decoders import IntDecoder
+    from ffcv_b200.transforms import ToTensor
+    kw.setdefault('pipelines', {'image': None, 'label': [IntDecoder(), ToTensor()]})
+    kw.setdefault('num_workers', 2)
+    return Loader(path, **kw)
+
+
+def test_sequential_batches_and_partial_last_batch(beton):
+    truth = _labels(beton)
+    loader = _loader(beton, batch_size=32, drop_last=False)
+    assert len(loader) == 7
+    got = [b[0].clone() for b in loader]  # batches are views of the slot ring: copy before it wraps
+    assert [g.shape for g in got] == [(32, 1)] * 6 + [(11, 1)]
+    assert np.array_equal(ch.cat(got).numpy().ravel(), truth)
+    loader = _loader(beton, batch_size=32, drop_last=True)
+    assert len(loader) == 6 and sum(b[0].shape[0] for b in loader) == 192
+
+
+def test_default_pipeline_and_disabled_field(beton):
+    from ffcv_b200 import Loader
+    # `label` gets the default pipeline (decoder + ToTensor); the image field is switched off
+    loader = Loader(beton, batch_size=50, num_workers=1, pipelines={'image': None})
+    batch = next(iter(loader))
+    assert len(batch) == 1 and isinstance(batch[0], ch.Tensor) and batch[0].dtype == ch.int64
+
+
+def test_random_order_changes_per_epoch_and_is_seeded(beton):
+    from ffcv_b200 import OrderOption
+    truth = _labels(beton)
+    a = _loader(beton, batch_size=64, order=OrderOption.RANDOM, seed=5, drop_last=False)
+    b = _loader(beton, batch_size=64, order=OrderOption.RANDOM, seed=5, drop_last=False)
+    e0 = ch.cat([x[0].clone() for x in a]).numpy().ravel()
+    e1 = ch.cat([x[0].clone() for x in a]).numpy().ravel()
+    f0 = ch.cat([x[0].clone() for x in b]).numpy().ravel()
+    assert np.array_equal(e0, f0) and not np.array_equal(e0, e1)
+    assert np.array_equal(np.sort(e0), np.sort(truth))
+    order = np.random.default_rng(5).permutation(np.arange(203))
+    assert np.array_equal(e0, truth[order])
+
+
+def test_indices_subset_and_quasi_random(beton):
+    from ffcv_b200 import OrderOption
+    truth = _labels(beton)
+    idx = np.arange(3, 203, 5)
+    loader = _loader(beton, batch_size=16, indices=idx, drop_last=False)
+    assert np.array_equal(ch.cat([b[0].clone() for b in loader]).numpy().ravel(), truth[idx])
+    loader = _loader(beton, batch_size=16, indices=idx, order=OrderOption.QUASI_RANDOM, seed=1, drop_last=False)
+    got = ch.cat([b[0].clone() for b in loader]).numpy().ravel()
+    assert len(got) == len(idx) and np.array_equal(np.sort(got), np.sort(truth[idx]))
+
+
+def test_filter_builds_a_subset_loader(beton):
+    truth = _labels(beton)
+    loader = _loader(beton, batch_size=40, drop_last=False)
+    even = loader.filter('label', lambda x: int(x) % 2 == 0)
+    got = ch.cat([b[0].clone() for b in even]).numpy().ravel()
+    assert np.array_equal(got, truth[truth % 2 == 0])
+
+
+def test_custom_operation_with_memory_and_indices(beton):
+    """A user operation obeying the reference contract: allocation query, `(input, memory, indices)`
+    call signature through `with_indices`."""
+    from ffcv_b200.fields.decoders import IntDecoder
+    from ffcv_b200.pipeline import AllocationQuery, Operation
+    from ffcv_b200.transforms import ToTensor
+
+    class AddIndex(Operation):
+        def generate_code(self):
+            def add(inp, dst, indices):
+                dst[:len(indices), 0] = inp[:, 0] * 2 + np.asarray(indices)
+                return dst[:len(indices)]
+            add.with_indices = True
+            return add
+
+        def declare_state_and_memory(self, previous_state):
+            return previous_state, AllocationQuery((1,), np.dtype('int64'))
+
+    truth = _labels(beton)
+    loader = _loader(beton, batch_size=25, drop_last=False,
+                     pipelines={'image': None, 'label': [IntDecoder(), AddIndex(), ToTensor()]})
+    got = ch.cat([b[0].clone() for b in loader]).numpy().ravel()
+    assert np.array_equal(got, truth * 2 + np.arange(203))
+
+
+def test_worker_exception_reaches_the_consumer(beton):
+    """The reference leaves the consumer blocked forever when the worker thread dies
+    (epoch_iterator.py:76-112,155); here the exception is re-raised in `__next__`."""
+    from ffcv_b200.fields.decoders import IntDecoder
+    from ffcv_b200.pipeline import Operation
+
+    class Boom(Operation):
+        def generate_code(self):
+            def boom(inp, dst):
+                if inp[0, 0] >= 0 and boom.calls >= 2:
+                    raise RuntimeError('transform failed on purpose')
+                boom.calls += 1
+                return inp
+            boom.calls = 0
+            return boom
+
+        def declare_state_and_memory(self, previous_state):
+            return replace(previous_state, jit_mode=False), None
+
+    loader = _loader(beton, batch_size=20, pipelines={'image': None, 'label': [IntDecoder(), Boom()]})
+    it = iter(loader)
+    next(it)
+    next(it)
+    with pytest.raises(RuntimeError, match='on purpose'):
+        next(it)
+    # the loader is usable again afterwards
+    loader2 = _loader(beton, batch_size=20)
+    assert sum(1 for _ in loader2) == 10
+
+
+def test_abandoned_epoch_is_retired(beton):
+    loader = _loader(beton, batch_size=10)
+    it = iter(loader)
+    next(it)
+    first = loader._live_iterator
+    second = iter(loader)
+    assert not first.is_alive() and second is loader._live_iterator
+    assert sum(1 for _ in second) == 20
+
+
+def test_invalid_arguments(beton):
+    from ffcv_b200 import Loader
+    with pytest.raises(ValueError):
+        Loader(beton, batch_size=8, order='shuffled', pipelines={'image': None})
+    with pytest.raises(ValueError):
+        Loader(beton, batch_size=8, pipelines={'image': None, 'label': 5})
