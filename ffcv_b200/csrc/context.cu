@@ -27,9 +27,15 @@ using namespace ffcvb;
 namespace {
 
 // ------------------------------------------------------------------ staging thread pool
+// Worker threads with two job lanes.  The synchronous lane (parallel_for) serves the header
+// parse of the batch being staged; the asynchronous lane carries the payload copy of the batch
+// staged before it, which keeps running while the caller goes on.  Workers drain the synchronous
+// lane first, so a parse never queues behind a copy.  Items are handed out under the mutex,
+// `grain` at a time.
 class Pool {
   public:
-    explicit Pool(int n) : stop_(false), generation_(0), pending_(0) {
+    enum Lane { kSync = 0, kAsync = 1 };
+    explicit Pool(int n) {
         for (int i = 0; i < n; i++) workers_.emplace_back([this] { loop(); });
     }
     ~Pool() {
@@ -41,83 +47,96 @@ class Pool {
         for (auto &t : workers_) t.join();
     }
     // Runs fn(i) for i in [0, n) on the pool and the calling thread; returns when all are done.
-    void parallel_for(int n, const std::function<void(int)> &fn) {
-        start(n, fn);
-        wait();
+    void parallel_for(int n, int grain, std::function<void(int)> fn) {
+        post(kSync, n, grain, std::move(fn), nullptr);
+        wait(kSync);
     }
-    // Hands fn(i), i in [0, n), to the pool threads and returns; wait() (which also lends the
-    // calling thread) must be called before the next start().
-    void start(int n, std::function<void(int)> fn) {
-        wait();
-        if (n <= 0) return;
-        job_ = std::move(fn);
-        if (workers_.empty()) {
-            n_ = n;
-            next_.store(0);
-            busy_ = true;
-            return; // wait() runs it
+    // Hands fn(i), i in [0, n), to the workers and returns.  `done` runs once after the last item
+    // (under the pool's mutex: it must be short and must not call the pool).  The lane must be idle.
+    // At most `max_threads` threads work on the job at a time (0 = no limit).
+    void post(Lane lane, int n, int grain, std::function<void(int)> fn, std::function<void()> done,
+              int max_threads = 0) {
+        wait(lane);
+        if (n <= 0) {
+            if (done) done();
+            return;
         }
         {
             std::lock_guard<std::mutex> g(m_);
-            fn_ = &job_;
-            n_ = n;
-            next_.store(0);
-            pending_ = (int)workers_.size();
-            generation_++;
+            Job &j = jobs_[lane];
+            j.fn = std::move(fn);
+            j.done = std::move(done);
+            j.n = n;
+            j.next = 0;
+            j.grain = grain < 1 ? 1 : grain;
+            j.inflight = 0;
+            j.limit = max_threads > 0 ? max_threads : 1 << 30;
+            j.active = true;
         }
-        busy_ = true;
-        cv_.notify_all();
+        if (workers_.empty())
+            wait(lane); // nobody else would run it
+        else
+            cv_.notify_all();
     }
-    void wait() {
-        if (!busy_) return;
-        if (workers_.empty()) {
-            fn_ = &job_;
-            drain();
-        } else {
-            drain();
-            std::unique_lock<std::mutex> g(m_);
-            done_cv_.wait(g, [this] { return pending_ == 0; });
+    // Lends the calling thread to the lane's job, then waits until the job is complete.
+    void wait(Lane lane) {
+        std::unique_lock<std::mutex> g(m_);
+        Job &j = jobs_[lane];
+        while (j.active) {
+            if (j.next < j.n)
+                run_some(j, g);
+            else
+                done_cv_.wait(g, [&] { return !j.active; });
         }
-        fn_ = nullptr;
-        busy_ = false;
+    }
+    void wait_all() {
+        wait(kSync);
+        wait(kAsync);
     }
     int size() const { return (int)workers_.size() + 1; }
 
   private:
-    void drain() {
-        for (;;) {
-            int i = next_.fetch_add(1);
-            if (i >= n_) break;
-            (*fn_)(i);
+    struct Job {
+        std::function<void(int)> fn;
+        std::function<void()> done;
+        int n = 0, next = 0, grain = 1, inflight = 0, limit = 1 << 30;
+        bool active = false;
+    };
+    // Called with the mutex held and items left; returns with it held.
+    void run_some(Job &j, std::unique_lock<std::mutex> &g) {
+        const int lo = j.next;
+        const int hi = lo + j.grain < j.n ? lo + j.grain : j.n;
+        j.next = hi;
+        j.inflight++;
+        g.unlock();
+        for (int i = lo; i < hi; i++) j.fn(i);
+        g.lock();
+        j.inflight--;
+        if (j.next >= j.n && j.inflight == 0) {
+            if (j.done) j.done();
+            j.done = nullptr;
+            j.active = false;
+            done_cv_.notify_all();
         }
     }
+    Job *pending() {
+        for (Job &j : jobs_)
+            if (j.active && j.next < j.n && j.inflight < j.limit) return &j;
+        return nullptr;
+    }
     void loop() {
-        uint64_t seen = 0;
+        std::unique_lock<std::mutex> g(m_);
         for (;;) {
-            {
-                std::unique_lock<std::mutex> g(m_);
-                cv_.wait(g, [&] { return stop_ || generation_ != seen; });
-                if (stop_) return;
-                seen = generation_;
-            }
-            drain();
-            {
-                std::lock_guard<std::mutex> g(m_);
-                if (--pending_ == 0) done_cv_.notify_all();
-            }
+            cv_.wait(g, [&] { return stop_ || pending() != nullptr; });
+            if (stop_) return;
+            while (Job *j = pending()) run_some(*j, g);
         }
     }
     std::vector<std::thread> workers_;
     std::mutex m_;
     std::condition_variable cv_, done_cv_;
-    bool stop_;
-    uint64_t generation_;
-    int pending_;
-    const std::function<void(int)> *fn_ = nullptr;
-    std::function<void(int)> job_;
-    bool busy_ = false; // touched by the owning (calling) thread only
-    int n_ = 0;
-    std::atomic<int> next_{0};
+    bool stop_ = false;
+    Job jobs_[2];
 };
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -162,7 +181,8 @@ struct Slot {
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes = 0, raw_bytes = 0, jpeg_bytes = 0;
     bool staged = false;
     bool direct = false; // payloads are gathered by the GPU from pinned host memory
-    bool copying = false; // the payload copy of the staged batch may still be running on the pool
+    size_t staged_end = 0; // blob bytes [0, staged_end) come from the pinned staging buffer
+    bool copy_done = true; // the staging threads have finished this slot's payload copy (guarded by ctx->copy_m)
     std::vector<ImageDesc> descs;
     std::vector<uint64_t> src_ptrs;
     double stage_ms[4] = {0, 0, 0, 0}; // header parse, layout, payload copy, total
@@ -171,7 +191,8 @@ struct Slot {
     // payload gather runs on its own high-priority stream so that its few CTAs are placed ahead of
     // the large grids other slots have queued, and the PCIe transfer overlaps their compute
     cudaStream_t gather_stream = nullptr;
-    cudaEvent_t ev_begin = nullptr, ev_gathered = nullptr;
+    cudaEvent_t ev_begin = nullptr, ev_gather_start = nullptr, ev_gathered = nullptr;
+    bool gather_timed = false; // ev_gather_start .. ev_gathered bracket the last gather of this slot
     bool timed = false; // events of the last run are valid
 };
 
@@ -185,15 +206,28 @@ struct AuxBuf {
 
 } // namespace
 
+struct WaitArg {
+    ffcvb_ctx *ctx;
+    int slot;
+};
+
 struct ffcvb_ctx {
     int device = 0;
     std::vector<Slot> slots;
+    std::vector<WaitArg> wait_args; // one per slot, for the stream callback that waits for its copy
+    std::mutex copy_m;
+    std::condition_variable copy_cv;
+    std::atomic<bool> copy_timeout{false};
     Pool *pool = nullptr;
     std::string err;
     AuxBuf aux[4];
     int aux_next = 0;
     bool profile = false;
     bool async_staging = false;
+    int cpu_share_permille = 0; // pinned source: share of the payload bytes the staging threads copy
+    bool adaptive_split = false; // ... adjusted from batch to batch so that both sides take equally long
+    double share = 0.0;          // the adjusted share, 0..1
+    int split_copy_threads = 4; // ... and how many of them copy at a time (more only crowd the gather out)
     DevBuf one_src, one_dst; // single-image entry points
 };
 
@@ -297,6 +331,7 @@ int ffcvb_create(int device, int n_slots, int n_threads, ffcvb_ctx **out) {
     ffcvb_ctx *c = new ffcvb_ctx();
     c->device = device;
     c->slots.resize(n_slots);
+    for (int i = 0; i < n_slots; i++) c->wait_args.push_back(WaitArg{c, i});
     c->pool = new Pool(n_threads - 1);
     *out = c;
     return FFCVB_OK;
@@ -304,7 +339,7 @@ int ffcvb_create(int device, int n_slots, int n_threads, ffcvb_ctx **out) {
 
 void ffcvb_destroy(ffcvb_ctx *ctx) {
     if (!ctx) return;
-    ctx->pool->wait();
+    ctx->pool->wait_all();
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
     for (auto &s : ctx->slots) {
@@ -316,6 +351,7 @@ void ffcvb_destroy(ffcvb_ctx *ctx) {
         if (s.gather_stream) cudaStreamDestroy(s.gather_stream);
         if (s.ev_begin) cudaEventDestroy(s.ev_begin);
         if (s.ev_gathered) cudaEventDestroy(s.ev_gathered);
+        if (s.ev_gather_start) cudaEventDestroy(s.ev_gather_start);
     }
     for (auto &a : ctx->aux) {
         if (a.dev.p) cudaFree(a.dev.p);
@@ -359,15 +395,21 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     }
     const bool direct = src_dev_base != 0;
     s.direct = direct;
-    ctx->pool->wait(); // a previous batch's copy may still use the pool
-    for (auto &o : ctx->slots) o.copying = false;
+    {   // a copy of this very slot that was never submitted may still be running
+        bool done;
+        {
+            std::lock_guard<std::mutex> g(ctx->copy_m);
+            done = s.copy_done;
+        }
+        if (!done) ctx->pool->wait(Pool::kAsync);
+    }
     std::vector<ImageDesc> &descs = s.descs;
     descs.assign(n, ImageDesc{});
     s.src_ptrs.assign(ptrs, ptrs + n);
     s.headers.resize(n);
 
     // ---- per-sample: parse headers, decide what to stage
-    ctx->pool->parallel_for(n, [&](int i) {
+    ctx->pool->parallel_for(n, 8, [&](int i) {
         ImageDesc &d = descs[i];
         memset(&d, 0, sizeof(d));
         d.mode = modes[i];
@@ -421,6 +463,35 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     });
 
     const auto t1 = std::chrono::steady_clock::now();
+    // Split staging: with a pinned source the staging threads (and the copy engine) can carry part
+    // of the bytes while the GPU gathers the rest, so that neither path alone has to fill the link.
+    // Samples are dealt to the CPU side greedily so that its share of the running byte count holds.
+    if (direct && ctx->adaptive_split) {
+        // The slot's previous batch tells how long its two halves took: the staging threads' copy
+        // (host clock) and the GPU's gather (events).  Move the share towards equal times; the
+        // step is small because the measurement is several batches old.
+        float tg = 0;
+        if (s.gather_timed && cudaEventElapsedTime(&tg, s.ev_gather_start, s.ev_gathered) == cudaSuccess) {
+            const double tc = s.staged_end > s.hdr.payload_off ? s.stage_ms[2] : 0.0;
+            if (tg + tc > 0) ctx->share += 0.04 * ((double)tg - tc) / ((double)tg + tc);
+            if (ctx->share < 0) ctx->share = 0;
+            if (ctx->share > 0.8) ctx->share = 0.8;
+        } else {
+            cudaGetLastError(); // not run yet, or still running: keep the share
+        }
+        s.gather_timed = false;
+        ctx->cpu_share_permille = (int)(ctx->share * 1000 + 0.5);
+    }
+    if (direct && ctx->cpu_share_permille > 0) {
+        uint64_t total = 0, cpu = 0;
+        for (int i = 0; i < n; i++) {
+            total += descs[i].payload_size;
+            if (cpu * 1000 < total * (uint64_t)ctx->cpu_share_permille) {
+                cpu += descs[i].payload_size;
+                descs[i].src_addr = 0;
+            }
+        }
+    }
     // ---- serial: deduplicate tables, lay the blob out
     std::vector<const RawHuff *> huff_src;
     std::vector<const uint16_t *> mult_src;
@@ -515,16 +586,26 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.seq_list_off = off;
     off = align_up(off + sizeof(int32_t) * seq_list.size(), 16);
     hd.payload_off = off;
+    // payloads the staging threads copy come first: they travel with the head of the blob
     for (int i = 0; i < n; i++) {
+        if (descs[i].src_addr != 0) continue;
+        descs[i].payload_off = off;
+        off = align_up(off + descs[i].payload_size, kPayloadAlign);
+    }
+    s.staged_end = off;
+    for (int i = 0; i < n; i++) {
+        if (descs[i].src_addr == 0) continue;
         // gathered payloads keep their source alignment mod 16 so both sides move in 16-byte words
         const bool rowwise = descs[i].mode == FFCVB_MODE_RAW && descs[i].cols != descs[i].width;
-        descs[i].payload_off = off + ((direct && !rowwise) ? (descs[i].src_addr & 15) : 0);
+        descs[i].payload_off = off + (rowwise ? 0 : (descs[i].src_addr & 15));
         off = align_up(descs[i].payload_off + descs[i].payload_size, kPayloadAlign);
     }
     hd.total_bytes = off;
 
     int rc;
-    if ((rc = grow_host(ctx, s.host, s.host_cap, (direct ? hd.payload_off : off) + 64))) return rc;
+    // The staging buffer is sized for the whole batch although a pinned source uses only part of
+    // it: the part varies from batch to batch, and regrowing page-locked memory stalls the device.
+    if ((rc = grow_host(ctx, s.host, s.host_cap, off + 64))) return rc;
     if ((rc = grow_dev(ctx, s.blob, off + 64))) return rc;
     if ((rc = grow_dev(ctx, s.clean, clean_bytes + 64))) return rc;
     if ((rc = grow_dev(ctx, s.coef, (size_t)total_blocks * 128 + 64))) return rc;
@@ -546,36 +627,48 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     const auto t2 = std::chrono::steady_clock::now();
     // ---- parallel: gather the payload bytes into pinned memory
     uint8_t *host = s.host;
-    if (!direct) {
+    if (s.staged_end > hd.payload_off) {
         Slot *sp = &s; // the job may outlive this call: it only touches slot-owned data and the source
-        ctx->pool->start(n, [sp, host, file_base](int i) {
-            const ImageDesc &d = sp->descs[i];
-            if (d.payload_size == 0) return;
-            const uint8_t *src = file_base + sp->src_ptrs[i];
-            uint8_t *dst = host + d.payload_off;
-            if (d.mode == FFCVB_MODE_RAW && d.cols != d.width) {
-                // only the crop box travels: one run per row.  Plain copies: streaming stores on
-                // ~1 KB rows leave partial write-combining lines and measured almost twice slower
-                const size_t pitch = (size_t)d.width * 3, run = (size_t)d.cols * 3;
-                src += (size_t)d.row0 * pitch + (size_t)d.col0 * 3;
-                for (int r = 0; r < d.rows; r++) memcpy(dst + r * (size_t)d.raw_pitch, src + r * pitch, run);
-            } else {
-                if (d.mode == FFCVB_MODE_RAW) src += (size_t)d.row0 * d.width * 3;
-                stream_copy(dst, src, d.payload_size);
-            }
-            _mm_sfence(); // streaming stores are weakly ordered: publish them before the batch is submitted
-        });
-        s.copying = true;
-        if (!ctx->async_staging) {
-            ctx->pool->wait();
-            s.copying = false;
+        ctx->pool->wait(Pool::kAsync); // one copy at a time: the batch staged before this one
+        int copy_threads = direct ? ctx->split_copy_threads : 0;
+        if (const char *e = getenv("FFCV_B200_COPY_THREADS")) copy_threads = atoi(e); // tuning override
+        {
+            std::lock_guard<std::mutex> g(ctx->copy_m);
+            s.copy_done = false;
         }
+        ctx->pool->post(
+            Pool::kAsync, n, 1,
+            [sp, host, file_base](int i) {
+                const ImageDesc &d = sp->descs[i];
+                if (d.payload_size == 0 || d.src_addr != 0) return;
+                const uint8_t *src = file_base + sp->src_ptrs[i];
+                uint8_t *dst = host + d.payload_off;
+                if (d.mode == FFCVB_MODE_RAW && d.cols != d.width) {
+                    // only the crop box travels: one run per row.  Plain copies: streaming stores on
+                    // ~1 KB rows leave partial write-combining lines and measured almost twice slower
+                    const size_t pitch = (size_t)d.width * 3, run = (size_t)d.cols * 3;
+                    src += (size_t)d.row0 * pitch + (size_t)d.col0 * 3;
+                    for (int r = 0; r < d.rows; r++) memcpy(dst + r * (size_t)d.raw_pitch, src + r * pitch, run);
+                } else {
+                    if (d.mode == FFCVB_MODE_RAW) src += (size_t)d.row0 * d.width * 3;
+                    stream_copy(dst, src, d.payload_size);
+                }
+                _mm_sfence(); // streaming stores are weakly ordered: publish them before the copy is reported done
+            },
+            [ctx, sp, t2] {
+                std::lock_guard<std::mutex> g(ctx->copy_m);
+                sp->stage_ms[2] = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t2).count();
+                sp->copy_done = true;
+                ctx->copy_cv.notify_all();
+            },
+            copy_threads);
+        if (!ctx->async_staging) ctx->pool->wait(Pool::kAsync);
     }
     const auto t3 = std::chrono::steady_clock::now();
     auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
     s.stage_ms[0] = ms(t0, t1);
     s.stage_ms[1] = ms(t1, t2);
-    s.stage_ms[2] = ms(t2, t3);
+    if (s.staged_end <= hd.payload_off) s.stage_ms[2] = 0; // else: written when the copy completes
     s.stage_ms[3] = ms(t0, t3);
     s.n_jpeg = (int)jpeg_list.size();
     s.n_par = (int)par_list.size();
@@ -610,7 +703,30 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     return FFCVB_OK;
 }
 
+// Stream callback: holds the stream until the staging threads have finished the slot's payload
+// copy, so that a batch can be queued while its bytes are still being staged.  Makes no CUDA call.
+// The wait is bounded; running out of time is recorded and reported by the next call.
+static void CUDART_CB wait_for_copy(void *arg) {
+    WaitArg *w = static_cast<WaitArg *>(arg);
+    ffcvb_ctx *c = w->ctx;
+    std::unique_lock<std::mutex> g(c->copy_m);
+    if (!c->copy_cv.wait_for(g, std::chrono::seconds(120), [&] { return c->slots[w->slot].copy_done; }))
+        c->copy_timeout.store(true);
+}
+
+static int hold_for_copy(ffcvb_ctx *ctx, Slot &s, cudaStream_t st) {
+    bool done;
+    {
+        std::lock_guard<std::mutex> g(ctx->copy_m);
+        done = s.copy_done;
+    }
+    if (!done) CU(cudaLaunchHostFunc(st, wait_for_copy, &ctx->wait_args[&s - ctx->slots.data()]));
+    return FFCVB_OK;
+}
+
 static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bool copy) {
+    if (ctx->copy_timeout.load())
+        return fail(ctx, FFCVB_E_CUDA, "a payload copy did not finish within its time limit: the batch that waited for it is invalid");
     const BatchHeader &hd = s.hdr;
     uint8_t *blob = (uint8_t *)s.blob.p;
     const bool prof = ctx->profile;
@@ -620,7 +736,9 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
             if (!e) CU(cudaEventCreate(&e));
         CU(cudaEventRecord(s.ev[0], st));
     }
+    int hrc;
     if (copy && !s.direct) {
+        if ((hrc = hold_for_copy(ctx, s, st))) return hrc;
         CU(cudaMemcpyAsync(blob, s.host, hd.total_bytes, cudaMemcpyHostToDevice, st));
     } else if (copy) {
         if (!s.gather_stream) {
@@ -628,13 +746,22 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
             CU(cudaDeviceGetStreamPriorityRange(&lo, &hi));
             CU(cudaStreamCreateWithPriority(&s.gather_stream, cudaStreamNonBlocking, hi));
             CU(cudaEventCreateWithFlags(&s.ev_begin, cudaEventDisableTiming));
-            CU(cudaEventCreateWithFlags(&s.ev_gathered, cudaEventDisableTiming));
+            CU(cudaEventCreate(&s.ev_gather_start));
+            CU(cudaEventCreate(&s.ev_gathered));
         }
         CU(cudaEventRecord(s.ev_begin, st)); // everything the caller ordered before this batch
         CU(cudaStreamWaitEvent(s.gather_stream, s.ev_begin, 0));
+
         CU(cudaMemcpyAsync(blob, s.host, hd.payload_off, cudaMemcpyHostToDevice, s.gather_stream));
+        CU(cudaEventRecord(s.ev_gather_start, s.gather_stream)); // after the head's copy: that one queues behind other batches' transfers
+        s.gather_timed = true;
         launch_gather_payloads(reinterpret_cast<const ImageDesc *>(blob + hd.desc_off), s.n, blob, s.gather_stream);
         CU(cudaEventRecord(s.ev_gathered, s.gather_stream));
+        if (s.staged_end > hd.payload_off) { // the CPU-staged share rides the copy engine meanwhile
+            if ((hrc = hold_for_copy(ctx, s, st))) return hrc;
+            CU(cudaMemcpyAsync(blob + hd.payload_off, s.host + hd.payload_off, s.staged_end - hd.payload_off,
+                               cudaMemcpyHostToDevice, st));
+        }
         CU(cudaStreamWaitEvent(st, s.ev_gathered, 0));
     }
     if (prof) CU(cudaEventRecord(s.ev[1], st));
@@ -677,11 +804,22 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
 
 int ffcvb_set_async_staging(ffcvb_ctx *ctx, int enabled) {
     if (!ctx) return FFCVB_E_ARG;
-    ctx->pool->wait();
-    for (auto &o : ctx->slots) o.copying = false;
+    ctx->pool->wait_all();
     ctx->async_staging = enabled != 0;
     return FFCVB_OK;
 }
+
+int ffcvb_set_staging_split(ffcvb_ctx *ctx, int cpu_share_permille) {
+    if (!ctx) return FFCVB_E_ARG;
+    if (cpu_share_permille < -1 || cpu_share_permille > 1000)
+        return fail(ctx, FFCVB_E_ARG, "ffcvb_set_staging_split: share must be 0..1000, or -1");
+    ctx->adaptive_split = cpu_share_permille < 0;
+    ctx->share = ctx->adaptive_split ? 0.3 : cpu_share_permille / 1000.0;
+    ctx->cpu_share_permille = (int)(ctx->share * 1000 + 0.5);
+    return FFCVB_OK;
+}
+
+int ffcvb_staging_split(const ffcvb_ctx *ctx) { return ctx ? ctx->cpu_share_permille : -1; }
 
 int ffcvb_set_profiling(ffcvb_ctx *ctx, int enabled) {
     if (!ctx) return FFCVB_E_ARG;
@@ -707,10 +845,6 @@ int ffcvb_submit_batch(ffcvb_ctx *ctx, int slot, void *stream, void *out_dev) {
         return fail(ctx, FFCVB_E_ARG, "ffcvb_submit_batch: bad argument");
     Slot &s = ctx->slots[slot];
     if (!s.staged) return fail(ctx, FFCVB_E_ARG, "ffcvb_submit_batch: slot %d has no staged batch", slot);
-    if (s.copying) { // asynchronous staging: the copy was left running
-        ctx->pool->wait();
-        s.copying = false;
-    }
     CU(cudaSetDevice(ctx->device));
     return run_batch(ctx, s, (cudaStream_t)stream, out_dev, true);
 }

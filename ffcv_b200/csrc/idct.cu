@@ -6,6 +6,8 @@
 // triangle ("fancy") chroma upsampler, and the 16.16 fixed-point YCbCr->RGB transform.  These are
 // integer butterflies in registers; they are not a dense contraction and must not be reordered,
 // so no tensor cores.
+#include <stdlib.h>
+
 #include "kernels.h"
 
 namespace ffcvb {
@@ -212,7 +214,12 @@ gather_payloads_kernel(const ImageDesc *__restrict__ descs, int n, uint8_t *__re
 
 void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, cudaStream_t stream) {
     if (n <= 0) return;
-    const int grid = n < 16 ? n : 16;
+    static const int ctas = [] {
+        const char *e = getenv("FFCV_B200_GATHER_CTAS"); // tuning override
+        const int v = e ? atoi(e) : 0;
+        return v > 0 && v <= 1024 ? v : 16;
+    }();
+    const int grid = n < ctas ? n : ctas;
     gather_payloads_kernel<<<grid, 256, 0, stream>>>(descs, n, blob);
 }
 

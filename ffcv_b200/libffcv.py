@@ -52,6 +52,10 @@ lib.ffcvb_rerun_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_rerun_batch.restype = c_int
 lib.ffcvb_set_async_staging.argtypes = [c_void_p, c_int]
 lib.ffcvb_set_async_staging.restype = c_int
+lib.ffcvb_set_staging_split.argtypes = [c_void_p, c_int]
+lib.ffcvb_set_staging_split.restype = c_int
+lib.ffcvb_staging_split.argtypes = [c_void_p]
+lib.ffcvb_staging_split.restype = c_int
 lib.ffcvb_set_profiling.argtypes = [c_void_p, c_int]
 lib.ffcvb_set_profiling.restype = c_int
 lib.ffcvb_batch_times.argtypes = [c_void_p, c_int, c_void_p]
@@ -152,6 +156,12 @@ class Context:
 
     def rerun(self, slot, stream, out_ptr):
         self._check(lib.ffcvb_rerun_batch(self._h, slot, stream or None, out_ptr), 'ffcvb_rerun_batch')
+
+    def set_staging_split(self, cpu_share_permille):
+        self._check(lib.ffcvb_set_staging_split(self._h, int(cpu_share_permille)), 'ffcvb_set_staging_split')
+
+    def staging_split(self):
+        return int(lib.ffcvb_staging_split(self._h))
 
     def set_async_staging(self, enabled):
         self._check(lib.ffcvb_set_async_staging(self._h, int(bool(enabled))), 'ffcvb_set_async_staging')

@@ -92,7 +92,7 @@ class Loader:
                  pipelines: Mapping[str, Sequence[Union[Operation, ch.nn.Module]]] = {},
                  custom_fields: Mapping[str, Type[Field]] = {}, drop_last: bool = True,
                  batches_ahead: int = 3, recompile: bool = False, order_kwargs: dict = dict(),
-                 pin_file: bool = None):
+                 pin_file: bool = None, cpu_stage_share: float = None):
         if distributed and order == OrderOption.RANDOM and (seed is None):
             print('Warning: no ordering seed was specified with distributed=True. '
                   'Setting seed to 0 to match PyTorch distributed sampler.')
@@ -104,7 +104,7 @@ class Loader:
             'fname': fname, 'batch_size': batch_size, 'num_workers': num_workers, 'os_cache': os_cache,
             'order': order, 'distributed': distributed, 'seed': seed, 'indices': indices,
             'pipelines': pipelines, 'drop_last': drop_last, 'batches_ahead': batches_ahead,
-            'recompile': recompile, 'pin_file': pin_file,
+            'recompile': recompile, 'pin_file': pin_file, 'cpu_stage_share': cpu_stage_share,
         }
         self.fname = fname
         self.batch_size = batch_size
@@ -131,6 +131,12 @@ class Loader:
             limit = float(environ.get('FFCV_B200_PIN_LIMIT_GB', '64')) * (1 << 30)
             pin_file = ch.cuda.is_available() and threads < 16 and getsize(fname) <= limit
         self.pin_file = bool(pin_file)
+        if cpu_stage_share is None and 'FFCV_B200_STAGE_SPLIT' in environ:
+            cpu_stage_share = int(environ['FFCV_B200_STAGE_SPLIT']) / 1000
+        if cpu_stage_share is not None and not 0 <= cpu_stage_share <= 1:
+            raise ValueError("cpu_stage_share must lie in [0, 1]")
+        # None: the native context balances the share from batch to batch
+        self.stage_split = -1 if cpu_stage_share is None else int(round(cpu_stage_share * 1000))
         self.memory_manager: MemoryManager = OSCacheManager(self.reader, pin=self.pin_file)
 
         if order in ORDER_MAP:
@@ -182,10 +188,14 @@ class Loader:
                                "no CUDA device is visible")
         index = device.index if device is not None and device.index is not None else ch.cuda.current_device()
         if index not in self._contexts:
-            self._contexts[index] = L.Context(index, n_slots=self.batches_ahead + 2,
-                                              n_threads=self.num_workers)
+            # With the file pinned the GPU fetches most bytes itself: a few staging threads carry
+            # the CPU's share, more of them only slow the gather down (measured).
+            threads = min(self.num_workers, 4) if self.pin_file else self.num_workers
+            self._contexts[index] = L.Context(index, n_slots=self.batches_ahead + 2, n_threads=threads)
             # the payload copy of a batch overlaps the drawing of the next batch's parameters
             self._contexts[index].set_async_staging(True)
+            if self.pin_file:
+                self._contexts[index].set_staging_split(self.stage_split)
         return self._contexts[index]
 
     def slot_streams(self):

@@ -103,10 +103,27 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                       const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params);
 
 /* With asynchronous staging enabled, ffcvb_stage_batch returns as soon as the batch is laid out
- * and leaves the payload copy running on the staging threads; ffcvb_submit_batch of that slot
- * waits for it.  The caller must keep `file_base` mapped until then and may use the time in
- * between to prepare the next batch.  Off by default. */
+ * and leaves the payload copy running on the staging threads.  ffcvb_submit_batch of that slot
+ * does not wait for it either: it queues a stream callback that holds `stream` until the copy is
+ * complete (at most 120 s; a copy that misses that limit makes every later submit fail with
+ * FFCVB_E_CUDA), then the host->device copy and the kernels, so the calling thread is free to
+ * stage the next batch while this one's bytes are still being copied; one copy runs at a time.
+ * The caller must keep `file_base` mapped until the batch has completed on the stream, and must
+ * not stage a slot again before its previous batch has completed.  Off by default. */
 int ffcvb_set_async_staging(ffcvb_ctx *ctx, int enabled);
+
+/* Split staging, for a `file_base` in page-locked memory (see ffcvb_stage_batch): the staging
+ * threads copy about `cpu_share_permille` / 1000 of every batch's payload bytes into the pinned
+ * staging buffer, which the copy engine moves, while the GPU gathers the rest over the link at
+ * the same time.  0 (the default) leaves everything to the gather; 1000 stages everything on the
+ * CPU; -1 starts at 300 and then adjusts the share from batch to batch so that the threads' copy
+ * and the GPU's gather of a batch take equally long (each slot's previous batch is the
+ * measurement).  At most four threads copy at a time in this mode: more of them slow the gather
+ * down.  Ignored for a pageable `file_base`.  No counterpart in the reference. */
+int ffcvb_set_staging_split(ffcvb_ctx *ctx, int cpu_share_permille);
+
+/* The share (per mille) the next batch will be staged with. */
+int ffcvb_staging_split(const ffcvb_ctx *ctx);
 
 /* Queue the staged batch on `stream`: one host->device copy of the staged bytes, then the decode
  * (entropy decode, dequantise + IDCT, chroma upsample + colour conversion) and the fused

@@ -74,17 +74,20 @@ def test_config1_lowres_jpeg_rrc160(datasets):
     compare_epoch(loader)
 
 
-@pytest.mark.parametrize('pin_file', [False, True], ids=['staged', 'pinned_gather'])
-def test_config2_fullres_mix_rrc224(datasets, pin_file):
-    """Both ways the bytes can reach the GPU: staged by CPU threads from the memory-mapped file
-    (crop box of raw samples only), and gathered by the GPU from a pinned copy of the file."""
+@pytest.mark.parametrize('pin_file,share', [(False, None), (True, 0.0), (True, 0.4), (True, 1.0)],
+                         ids=['staged', 'pinned_gather', 'pinned_split', 'pinned_all_cpu'])
+def test_config2_fullres_mix_rrc224(datasets, pin_file, share):
+    """The ways the bytes can reach the GPU: staged by CPU threads from the memory-mapped file
+    (crop box of raw samples only), gathered by the GPU from a pinned copy of the file, or split
+    between the two."""
     from ffcv_b200 import OrderOption
     from ffcv_b200.fields.decoders import RandomResizedCropRGBImageDecoder
     from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, ToTorchImage
     pipes = {'image': [RandomResizedCropRGBImageDecoder((224, 224)), RandomHorizontalFlip(),
                        NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()],
              'label': None}
-    loader = _loader(datasets[2], 32, pipes, order=OrderOption.QUASI_RANDOM, pin_file=pin_file)
+    loader = _loader(datasets[2], 32, pipes, order=OrderOption.QUASI_RANDOM, pin_file=pin_file,
+                     cpu_stage_share=share)
     assert loader.memory_manager.open() is not None and loader.memory_manager.pinned == pin_file
     modes = loader.reader.metadata['f0']['mode']
     assert 0 < modes.mean() < 1  # both raw and jpg samples present
