@@ -220,7 +220,7 @@ struct ffcvb_ctx {
     std::atomic<bool> copy_timeout{false};
     Pool *pool = nullptr;
     std::string err;
-    AuxBuf aux[4];
+    AuxBuf aux[16];
     int aux_next = 0;
     bool profile = false;
     bool async_staging = false;
@@ -914,6 +914,23 @@ int ffcvb_batch_status(ffcvb_ctx *ctx, int slot, void *stream, int32_t *status, 
     return bad;
 }
 
+// Small per-call parameter arrays travel through a ring of sixteen pinned/device buffer pairs: copies
+// `bytes` from `host` into the next pair (plus `extra` bytes of uninitialised device scratch behind
+// them) on `st`.  The caller records a->ev on `st` once its kernels are queued.
+static int stage_aux(ffcvb_ctx *ctx, cudaStream_t st, const void *host, size_t bytes, size_t extra, AuxBuf **out) {
+    AuxBuf &a = ctx->aux[ctx->aux_next];
+    ctx->aux_next = (ctx->aux_next + 1) % 16;
+    if (!a.ev) CU(cudaEventCreateWithFlags(&a.ev, cudaEventDisableTiming));
+    if (a.used) CU(cudaEventSynchronize(a.ev));
+    int rc;
+    if ((rc = grow_dev(ctx, a.dev, bytes + extra))) return rc;
+    if ((rc = grow_host(ctx, a.host, a.host_cap, bytes))) return rc;
+    memcpy(a.host, host, bytes);
+    CU(cudaMemcpyAsync(a.dev.p, a.host, bytes, cudaMemcpyHostToDevice, st));
+    *out = &a;
+    return FFCVB_OK;
+}
+
 int ffcvb_transform_device(ffcvb_ctx *ctx, void *stream, const uint8_t *src_dev, int n, int h, int w,
                            const ffcvb_plan *plan, const int32_t *params, void *out_dev) {
     if (!ctx) return FFCVB_E_ARG;
@@ -923,15 +940,10 @@ int ffcvb_transform_device(ffcvb_ctx *ctx, void *stream, const uint8_t *src_dev,
     cudaStream_t st = (cudaStream_t)stream;
     const int n_params = 4 + 2 * plan->n_ops;
     const size_t bytes = sizeof(int32_t) * (size_t)n * n_params;
-    AuxBuf &a = ctx->aux[ctx->aux_next];
-    ctx->aux_next = (ctx->aux_next + 1) % 4;
-    if (!a.ev) CU(cudaEventCreateWithFlags(&a.ev, cudaEventDisableTiming));
-    if (a.used) CU(cudaEventSynchronize(a.ev));
+    AuxBuf *ap;
     int rc;
-    if ((rc = grow_dev(ctx, a.dev, bytes))) return rc;
-    if ((rc = grow_host(ctx, a.host, a.host_cap, bytes))) return rc;
-    memcpy(a.host, params, bytes);
-    CU(cudaMemcpyAsync(a.dev.p, a.host, bytes, cudaMemcpyHostToDevice, st));
+    if ((rc = stage_aux(ctx, st, params, bytes, 0, &ap))) return rc;
+    AuxBuf &a = *ap;
     ResizeSource src{};
     src.uniform = src_dev;
     src.uniform_h = h;
@@ -941,6 +953,68 @@ int ffcvb_transform_device(ffcvb_ctx *ctx, void *stream, const uint8_t *src_dev,
     CU(cudaGetLastError());
     CU(cudaEventRecord(a.ev, st));
     a.used = true;
+    return FFCVB_OK;
+}
+
+int ffcvb_color_jitter(ffcvb_ctx *ctx, void *stream, uint8_t *images_dev, int n, int h, int w, int kind,
+                       const uint8_t *apply, const double *ratio) {
+    if (!ctx) return FFCVB_E_ARG;
+    if (!images_dev || n <= 0 || h <= 0 || w <= 0 || kind < 0 || kind > 2 || !apply || !ratio ||
+        (int64_t)h * w > (int64_t)1 << 30)
+        return fail(ctx, FFCVB_E_ARG, "ffcvb_color_jitter: bad argument");
+    CU(cudaSetDevice(ctx->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    // [ratio: n doubles][apply: n bytes, padded][grey sums: n counters (device only)]
+    const size_t apply_off = sizeof(double) * (size_t)n, sums_off = align_up(apply_off + n, 8);
+    std::vector<uint8_t> pack(sums_off, 0);
+    memcpy(pack.data(), ratio, sizeof(double) * (size_t)n);
+    memcpy(pack.data() + apply_off, apply, (size_t)n);
+    AuxBuf *a;
+    int rc;
+    if ((rc = stage_aux(ctx, st, pack.data(), sums_off, sizeof(unsigned long long) * (size_t)n, &a))) return rc;
+    uint8_t *dev = (uint8_t *)a->dev.p;
+    launch_color_jitter(images_dev, n, h, w, kind, dev + apply_off, (const double *)dev,
+                        (unsigned long long *)(dev + sums_off), st);
+    CU(cudaGetLastError());
+    CU(cudaEventRecord(a->ev, st));
+    a->used = true;
+    return FFCVB_OK;
+}
+
+int ffcvb_mixup(ffcvb_ctx *ctx, void *stream, const uint8_t *src_dev, uint8_t *dst_dev, int n, int64_t count,
+                const double *lam) {
+    if (!ctx) return FFCVB_E_ARG;
+    if (!src_dev || !dst_dev || src_dev == dst_dev || n <= 0 || count <= 0 || !lam)
+        return fail(ctx, FFCVB_E_ARG, "ffcvb_mixup: bad argument");
+    for (int i = 0; i < n; i++)
+        if (!(lam[i] >= 0.0 && lam[i] <= 1.0)) return fail(ctx, FFCVB_E_ARG, "ffcvb_mixup: lam[%d] outside [0, 1]", i);
+    CU(cudaSetDevice(ctx->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    AuxBuf *a;
+    int rc;
+    if ((rc = stage_aux(ctx, st, lam, sizeof(double) * (size_t)n, 0, &a))) return rc;
+    launch_mixup(src_dev, dst_dev, n, (long long)count, (const double *)a->dev.p, st);
+    CU(cudaGetLastError());
+    CU(cudaEventRecord(a->ev, st));
+    a->used = true;
+    return FFCVB_OK;
+}
+
+int ffcvb_poison(ffcvb_ctx *ctx, void *stream, uint8_t *images_dev, int n, int64_t count, const uint8_t *apply,
+                 const double *one_minus_alpha_dev, const double *mask_dev, double clamp_lo, double clamp_hi) {
+    if (!ctx) return FFCVB_E_ARG;
+    if (!images_dev || n <= 0 || count <= 0 || !apply || !one_minus_alpha_dev || !mask_dev || !(clamp_lo <= clamp_hi))
+        return fail(ctx, FFCVB_E_ARG, "ffcvb_poison: bad argument");
+    CU(cudaSetDevice(ctx->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    AuxBuf *a;
+    int rc;
+    if ((rc = stage_aux(ctx, st, apply, (size_t)n, 0, &a))) return rc;
+    launch_poison(images_dev, n, (long long)count, (const uint8_t *)a->dev.p, one_minus_alpha_dev, mask_dev,
+                  (float)clamp_lo, (float)clamp_hi, st);
+    CU(cudaGetLastError());
+    CU(cudaEventRecord(a->ev, st));
+    a->used = true;
     return FFCVB_OK;
 }
 

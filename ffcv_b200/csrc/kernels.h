@@ -48,4 +48,20 @@ void launch_resize_augment(const ResizeSource &src, int n, const int32_t *params
                            const OpList &ops, int resize, int out_h, int out_w, int out_kind,
                            const void *lut, void *out, const int32_t *status, cudaStream_t stream);
 
+// Colour jitter kinds (ffcv/transforms/color_jitter.py).
+enum { kJitterBrightness = 0, kJitterContrast = 1, kJitterSaturation = 2 };
+
+// Brightness / contrast / saturation of the images of a uint8 [n, h, w, 3] batch whose apply[i]
+// is non-zero, in place, with factor ratio[i].  grey_sum: n scratch counters (contrast only).
+void launch_color_jitter(uint8_t *images, int n, int h, int w, int kind, const uint8_t *apply,
+                         const double *ratio, unsigned long long *grey_sum, cudaStream_t stream);
+
+// dst[i] = lam[i] * src[i] + (1 - lam[i]) * src[i - 1] over `count` uint8 values per image.
+void launch_mixup(const uint8_t *src, uint8_t *dst, int n, long long count, const double *lam,
+                  cudaStream_t stream);
+
+// images[i] = clamp(images[i] * one_minus_alpha + mask) for the images with apply[i] != 0.
+void launch_poison(uint8_t *images, int n, long long count, const uint8_t *apply, const double *one_minus_alpha,
+                   const double *mask, float lo, float hi, cudaStream_t stream);
+
 } // namespace ffcvb

@@ -52,6 +52,13 @@ lib.ffcvb_rerun_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_rerun_batch.restype = c_int
 lib.ffcvb_set_async_staging.argtypes = [c_void_p, c_int]
 lib.ffcvb_set_async_staging.restype = c_int
+lib.ffcvb_color_jitter.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+lib.ffcvb_color_jitter.restype = c_int
+lib.ffcvb_mixup.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p]
+lib.ffcvb_mixup.restype = c_int
+lib.ffcvb_poison.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p,
+                             ctypes.c_double, ctypes.c_double]
+lib.ffcvb_poison.restype = c_int
 lib.ffcvb_set_staging_split.argtypes = [c_void_p, c_int]
 lib.ffcvb_set_staging_split.restype = c_int
 lib.ffcvb_staging_split.argtypes = [c_void_p]
@@ -159,6 +166,24 @@ class Context:
 
     def set_staging_split(self, cpu_share_permille):
         self._check(lib.ffcvb_set_staging_split(self._h, int(cpu_share_permille)), 'ffcvb_set_staging_split')
+
+    def color_jitter(self, stream_ptr, images_ptr, n, h, w, kind, apply, ratio):
+        apply = np.ascontiguousarray(apply, dtype=np.uint8)
+        ratio = np.ascontiguousarray(ratio, dtype=np.float64)
+        assert apply.shape == (n,) and ratio.shape == (n,)
+        self._check(lib.ffcvb_color_jitter(self._h, stream_ptr, images_ptr, n, h, w, kind, apply.ctypes.data,
+                                           ratio.ctypes.data), 'ffcvb_color_jitter')
+
+    def mixup(self, stream_ptr, src_ptr, dst_ptr, n, count, lam):
+        lam = np.ascontiguousarray(lam, dtype=np.float64)
+        assert lam.shape == (n,)
+        self._check(lib.ffcvb_mixup(self._h, stream_ptr, src_ptr, dst_ptr, n, count, lam.ctypes.data), 'ffcvb_mixup')
+
+    def poison(self, stream_ptr, images_ptr, n, count, apply, one_minus_alpha_ptr, mask_ptr, lo, hi):
+        apply = np.ascontiguousarray(apply, dtype=np.uint8)
+        assert apply.shape == (n,)
+        self._check(lib.ffcvb_poison(self._h, stream_ptr, images_ptr, n, count, apply.ctypes.data,
+                                     one_minus_alpha_ptr, mask_ptr, float(lo), float(hi)), 'ffcvb_poison')
 
     def staging_split(self):
         return int(lib.ffcvb_staging_split(self._h))

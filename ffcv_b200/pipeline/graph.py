@@ -160,6 +160,9 @@ class Graph:
                              self.metadata[f'f{p.f_ix}'], storage_state)
                 first = 1
             for k in range(first, len(p.ops)):
+                begin = getattr(p.ops[k], 'begin_batch', None)
+                if begin is not None:  # operations that draw random numbers of their own
+                    begin(self.seed, epoch, batch_ix, pi * 64 + k)
                 code = p.codes[k - p.n_fused]
                 mem = self._select(buffers[(pi, k)], slot, n)
                 if getattr(code, 'with_indices', False):

@@ -106,3 +106,30 @@ def sample_cutouts(seed, n, height, width, crop_size, out):
     for k in range(n):
         out[k, 0] = np.random.randint(height - crop_size + 1)
         out[k, 1] = np.random.randint(width - crop_size + 1)
+
+
+@njit(**_JIT)
+def sample_jitter(seed, n, p, low, high, apply, ratio):
+    # the two vector draws of ffcv/transforms/color_jitter.py:44-45 (:86-87, :124-125), in that order
+    np.random.seed(seed)
+    chosen = np.random.rand(n) < p
+    magnitudes = np.random.uniform(low, high, n)
+    for k in range(n):
+        apply[k] = 1 if chosen[k] else 0
+        ratio[k] = magnitudes[k]
+
+
+@njit(**_JIT)
+def sample_mixup(seed, alpha, same_lambda, out):
+    # ffcv/transforms/mixup.py:42-45 (:76-79): seeded with the last sample index of the batch, one
+    # beta draw for the whole batch or one per sample
+    np.random.seed(seed)
+    n = out.shape[0]
+    if same_lambda:
+        lam = np.random.beta(alpha, alpha)
+        for k in range(n):
+            out[k] = lam
+    else:
+        lams = np.random.beta(alpha, alpha, n)
+        for k in range(n):
+            out[k] = lams[k]

@@ -168,6 +168,34 @@ int ffcvb_batch_status(ffcvb_ctx *ctx, int slot, void *stream, int32_t *status, 
 int ffcvb_transform_device(ffcvb_ctx *ctx, void *stream, const uint8_t *src_dev, int n, int h,
                            int w, const ffcvb_plan *plan, const int32_t *params, void *out_dev);
 
+/* ---- colour and blending transforms on uint8 device batches -------------------------------
+ * Replacements of the numba closures of ffcv/transforms/color_jitter.py, mixup.py and
+ * poisoning.py.  `images_dev` / `src_dev` / `dst_dev` are DEVICE pointers to [n, h, w, 3] (or
+ * [n, count]) uint8 batches; the small per-image arrays are HOST pointers and are copied by the
+ * call.  All calls queue their work on `stream` and return. */
+#define FFCVB_JITTER_BRIGHTNESS 0
+#define FFCVB_JITTER_CONTRAST 1
+#define FFCVB_JITTER_SATURATION 2
+
+/* RandomBrightness / RandomContrast / RandomSaturation (color_jitter.py:41-50, :83-94,
+ * :121-136), in place: image i is changed when apply[i] != 0, with blend factor ratio[i].  The
+ * float64 arithmetic, including which multiply-adds are fused, is that of the reference's
+ * compiled code. */
+int ffcvb_color_jitter(ffcvb_ctx *ctx, void *stream, uint8_t *images_dev, int n, int h, int w, int kind,
+                       const uint8_t *apply, const double *ratio);
+
+/* ImageMixup (mixup.py:41-50): dst[i] = lam[i] * src[i] + (1 - lam[i]) * src[i - 1] over `count`
+ * values per image, image -1 being image n - 1; 0 <= lam[i] <= 1; dst must not be src. */
+int ffcvb_mixup(ffcvb_ctx *ctx, void *stream, const uint8_t *src_dev, uint8_t *dst_dev, int n, int64_t count,
+                const double *lam);
+
+/* Poison (poisoning.py:45-60), in place on the images with apply[i] != 0:
+ * clamp(image * one_minus_alpha + mask) evaluated through a float32 scratch value as the
+ * reference does.  one_minus_alpha_dev and mask_dev are DEVICE arrays of `count` doubles (the
+ * opacity repeated over the channels; the mask already multiplied by the opacity). */
+int ffcvb_poison(ffcvb_ctx *ctx, void *stream, uint8_t *images_dev, int n, int64_t count, const uint8_t *apply,
+                 const double *one_minus_alpha_dev, const double *mask_dev, double clamp_lo, double clamp_hi);
+
 /* ---- decode without allocating -----------------------------------------------------------
  * No counterpart in the reference.  For callers that must not allocate GPU memory while they
  * run: a process that handed all device memory to its own pool at start-up, a plugin living

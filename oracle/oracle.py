@@ -19,7 +19,7 @@ OUT_U8_NHWC, OUT_F16_NHWC, OUT_F16_NCHW, OUT_F32_NHWC, OUT_F32_NCHW = range(5)
 
 
 def build(force=False):
-    srcs = [os.path.join(HERE, f) for f in ('jpeg_oracle.c', 'resize_oracle.c', 'pipeline_oracle.c')]
+    srcs = [os.path.join(HERE, f) for f in ('jpeg_oracle.c', 'resize_oracle.c', 'pipeline_oracle.c', 'pixel_oracle.c')]
     stale = force or not os.path.exists(LIB_PATH) or any(
         os.path.getmtime(s) > os.path.getmtime(LIB_PATH) for s in srcs)
     if stale:
@@ -48,6 +48,13 @@ def lib():
         L.oracle_normalize.argtypes = [vp, ci, ci, vp, ci, vp]
         L.oracle_normalize.restype = None
         L.oracle_run_batch.argtypes = [ci, vp, vp, vp, ci, ci, vp, ci, vp, ci, vp, ci, vp]
+        for name in ('oracle_brightness', 'oracle_contrast', 'oracle_saturation'):
+            getattr(L, name).argtypes = [vp, ci, ci, ci, vp, vp]
+            getattr(L, name).restype = None
+        L.oracle_mixup.argtypes = [vp, vp, ci, sz, vp]
+        L.oracle_mixup.restype = None
+        L.oracle_poison.argtypes = [vp, ci, sz, vp, vp, vp, ctypes.c_double, ctypes.c_double]
+        L.oracle_poison.restype = None
         _lib = L
     return _lib
 
@@ -157,3 +164,43 @@ def run_batch(payloads, modes, heights, widths, crops, resize, out_h, out_w, ops
     lib().oracle_run_batch(n, ptrs, sizes.ctypes.data, desc.ctypes.data, out_h, out_w, ops.ctypes.data,
                            nops, lut_ptr, out_kind, out.ctypes.data, nthreads, status.ctypes.data)
     return out, status
+
+
+JITTER_BRIGHTNESS, JITTER_CONTRAST, JITTER_SATURATION = 0, 1, 2
+
+
+def color_jitter(images, kind, apply, ratio):
+    """Brightness / contrast / saturation of ffcv/transforms/color_jitter.py on a uint8
+    [n, h, w, 3] batch; returns a new array.  apply: bool per image, ratio: float64 per image."""
+    out = np.ascontiguousarray(images, dtype=np.uint8).copy()
+    n, h, w, c = out.shape
+    assert c == 3
+    apply = np.ascontiguousarray(apply, dtype=np.uint8)
+    ratio = np.ascontiguousarray(ratio, dtype=np.float64)
+    assert apply.shape == (n,) and ratio.shape == (n,)
+    fn = (lib().oracle_brightness, lib().oracle_contrast, lib().oracle_saturation)[kind]
+    fn(out.ctypes.data, n, h, w, apply.ctypes.data, ratio.ctypes.data)
+    return out
+
+
+def mixup(images, lam):
+    """ImageMixup of ffcv/transforms/mixup.py:41-50: image i blended with image i - 1."""
+    src = np.ascontiguousarray(images, dtype=np.uint8)
+    n = src.shape[0]
+    lam = np.ascontiguousarray(np.broadcast_to(np.asarray(lam, dtype=np.float64), (n,)))
+    out = np.empty_like(src)
+    lib().oracle_mixup(src.ctypes.data, out.ctypes.data, n, src[0].size, lam.ctypes.data)
+    return out
+
+
+def poison(images, apply, mask, alpha, clamp=(0, 255)):
+    """Poison of ffcv/transforms/poisoning.py:36-60.  mask: [h, w, 3], alpha: [h, w]."""
+    out = np.ascontiguousarray(images, dtype=np.uint8).copy()
+    n = out.shape[0]
+    alpha3 = np.repeat(np.asarray(alpha)[:, :, None], 3, axis=2)
+    m = np.ascontiguousarray(np.asarray(mask).astype('float') * alpha3, dtype=np.float64)
+    oma = np.ascontiguousarray(1 - alpha3, dtype=np.float64)
+    apply = np.ascontiguousarray(apply, dtype=np.uint8)
+    lib().oracle_poison(out.ctypes.data, n, out[0].size, apply.ctypes.data, oma.ctypes.data, m.ctypes.data,
+                        float(clamp[0]), float(clamp[1]))
+    return out

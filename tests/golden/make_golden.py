@@ -16,6 +16,13 @@ crop_cases.npz    crop boxes from the reference's own get_random_crop / get_cent
                   generation time, run under numpy's legacy seeded stream).
 normalize_cases.npz lookup tables built by the reference's NormalizeImage expression
                   (ffcv/transforms/normalize.py:42-43).
+pixel_cases.npz   outputs of the reference's own RandomBrightness / RandomContrast /
+                  RandomSaturation / ImageMixup / LabelMixup / Poison closures
+                  (ffcv/transforms/color_jitter.py, mixup.py, poisoning.py), imported from
+                  /root/reference and compiled by the reference's Compiler with one thread (with
+                  more, numba parallelises even the per-batch random draws and the result is not
+                  reproducible), numba's random stream seeded before each call; the draws
+                  themselves (made by the same calls in the same order) are stored beside them.
 """
 import ast
 import io
@@ -149,10 +156,117 @@ def normalize_cases():
     np.savez_compressed(os.path.join(HERE, 'normalize_cases.npz'), **out)
 
 
+def import_reference_transforms():
+    """The reference's transform modules without its package __init__ (which loads the compiled
+    extension that cannot be built here): a bare package object pointing at its source tree."""
+    import importlib
+    import types
+    pkg = types.ModuleType('ffcv')
+    pkg.__path__ = ['/root/reference/ffcv']
+    sys.modules['ffcv'] = pkg
+    stub = types.ModuleType('ffcv.libffcv')
+    stub.ctypes_resize = stub.imdecode = stub.memcpy = stub.resize_crop = None
+    sys.modules['ffcv.libffcv'] = stub
+    importlib.import_module('ffcv.pipeline')
+    mods = [importlib.import_module('ffcv.transforms.' + m) for m in ('color_jitter', 'mixup', 'poisoning')]
+    from ffcv.pipeline.compiler import Compiler
+    Compiler.set_enabled(True)
+    Compiler.set_num_threads(1)
+    return mods, Compiler
+
+
+def pixel_cases():
+    from numba import njit
+    (cj, mx, po), Compiler = import_reference_transforms()
+
+    @njit
+    def seed_numba(s):
+        np.random.seed(s)
+
+    # the draw helpers are compiled by the reference's own Compiler (fastmath etc.), like the closures
+    def jitter_draws(s, n, p, lo, hi):
+        np.random.seed(s)
+        apply = np.random.rand(n) < p
+        mags = np.random.uniform(lo, hi, n)
+        return apply, mags
+
+    def beta_draws(s, alpha, n):
+        np.random.seed(s)
+        return np.random.beta(alpha, alpha, n)
+
+    def beta_draw(s, alpha):
+        np.random.seed(s)
+        return np.random.beta(alpha, alpha)
+
+    jitter_draws, beta_draws, beta_draw = (Compiler.compile(f) for f in (jitter_draws, beta_draws, beta_draw))
+
+    rng = np.random.default_rng(77)
+    n, h, w = 10, 24, 28
+    images = np.stack([smooth(rng, h, w) for _ in range(n)])
+    images[1] = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+    images[2] = 255
+    images[3] = 0
+    out = {'images': images}
+    k = 0
+    for cls, name in [(cj.RandomBrightness, 'brightness'), (cj.RandomContrast, 'contrast'),
+                      (cj.RandomSaturation, 'saturation')]:
+        for magnitude, p, seed in [(0.5, 0.7, 11), (1.5, 1.0, 12), (0.1, 0.5, 13)]:
+            code = Compiler.compile(cls(magnitude, p).generate_code())
+            seed_numba(seed)
+            res = code(images.copy(), None)
+            apply, mags = jitter_draws(seed, n, p, max(0, 1 - magnitude), 1 + magnitude)
+            out[f'jitter_{k}_kind'] = np.array(name)
+            out[f'jitter_{k}_args'] = np.array([magnitude, p, seed])
+            out[f'jitter_{k}_apply'] = apply
+            out[f'jitter_{k}_ratio'] = mags
+            out[f'jitter_{k}_out'] = res
+            k += 1
+    out['jitter_count'] = np.array(k)
+    k = 0
+    for alpha, same, last_index in [(0.5, True, 41), (0.5, False, 42), (2.0, False, 43)]:
+        indices = np.arange(last_index - n + 1, last_index + 1)
+        code = Compiler.compile(mx.ImageMixup(alpha, same).generate_code())
+        res = code(images.copy(), np.zeros_like(images), indices)
+        labels = rng.integers(0, 1000, (n, 1)).astype(np.int64)
+        lcode = Compiler.compile(mx.LabelMixup(alpha, same).generate_code())
+        lres = lcode(labels.copy(), np.zeros((n, 3), np.float32), indices)
+        lam = np.full(n, beta_draw(last_index, alpha)) if same else beta_draws(last_index, alpha, n)
+        out[f'mixup_{k}_args'] = np.array([alpha, float(same), last_index])
+        out[f'mixup_{k}_lam'] = lam
+        out[f'mixup_{k}_out'] = res
+        out[f'mixup_{k}_labels'] = labels
+        out[f'mixup_{k}_labels_out'] = lres
+        k += 1
+    out['mixup_count'] = np.array(k)
+    mask = rng.integers(0, 256, (h, w, 3)).astype(np.uint8)
+    alpha = rng.uniform(0, 1, (h, w))
+    alpha[:4] = 0
+    alpha[-4:] = 1
+    poisoned = np.array([2, 5, 103, 107])
+    indices = np.arange(100, 100 + n)
+    k = 0
+    for clamp in [(0, 255), (30, 200)]:
+        code = Compiler.compile(po.Poison(mask, alpha, poisoned, clamp).generate_code())
+        res = code(images.copy(), np.zeros(images.shape, np.float32), indices)
+        out[f'poison_{k}_clamp'] = np.array(clamp)
+        out[f'poison_{k}_out'] = res
+        k += 1
+    out['poison_count'] = np.array(k)
+    out['poison_mask'] = mask
+    out['poison_alpha'] = alpha
+    out['poison_indices'] = poisoned
+    out['poison_batch_indices'] = indices
+    np.savez_compressed(os.path.join(HERE, 'pixel_cases.npz'), **out)
+
+
 if __name__ == '__main__':
+    if 'pixel' in sys.argv[1:]:
+        pixel_cases()
+        raise SystemExit
     jpeg_cases()
     resize_cases()
     crop_cases()
     normalize_cases()
+    pixel_cases()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))
