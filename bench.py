@@ -254,10 +254,19 @@ def main_ours(args):
 
     from ffcv_b200 import Loader, OrderOption
 
-    def make_loader(pin):
+    def make_loader(pin, share=None):
         return Loader(path, batch_size=BATCH, order=OrderOption.QUASI_RANDOM, distributed=world > 1, seed=0,
                       num_workers=workers, pipelines=build_pipelines(device), batches_ahead=args.batches_ahead,
-                      drop_last=True, pin_file=pin)
+                      drop_last=True, pin_file=pin, cpu_stage_share=share)
+
+    def describe(ld):
+        if not ld.memory_manager.pinned:
+            return 'file memory-mapped, staged into pinned buffers by CPU threads, one DMA copy per batch'
+        if ld.stage_split == 0:
+            return 'file in pinned host RAM, payloads gathered by the GPU over PCIe'
+        return ('file in pinned host RAM: the GPU gathers most payload bytes over PCIe, up to 4 CPU threads and the '
+                'copy engine carry the rest (share %s)' % ('balanced per batch' if ld.stage_split < 0
+                                                           else '%.2f' % (ld.stage_split / 1000)))
 
     def run_e2e(loader, sampler=None):
         exe = loader.graph.pipelines[0].executor
@@ -288,21 +297,30 @@ def main_ours(args):
         return e0.elapsed_time(e1), int(np.mean(h2d)), exe.launches, digest
 
     # ------------------------------------------------------------------ end to end (public API)
-    # Both ways the bytes can reach the GPU are timed; `e2e` is the one Loader picks by itself for
-    # this host (pin_file=None: GPU gather when a rank has fewer than 16 staging threads).
-    auto_pin = make_loader(None).memory_manager.pin
-    other = make_loader(not auto_pin)
-    other_ms, other_h2d, _, _ = run_e2e(other)
-    del other
+    # `e2e` is the mode Loader picks by itself on this host (pin_file=None, cpu_stage_share=None);
+    # the other ways the bytes can reach the GPU are timed beside it.
+    auto = make_loader(None)
+    auto_mode = (auto.pin_file, auto.stage_split)
+    del auto
+    others = {}
+    for name, pin, share in [('e2e_staged', False, None), ('e2e_gather', True, 0.0), ('e2e_split', True, None)]:
+        probe = make_loader(pin, share)
+        if (probe.pin_file, probe.stage_split) == auto_mode or (name == 'e2e_split' and probe.stage_split == 0):
+            del probe
+            continue
+        ms, h2d, _, _ = run_e2e(probe)
+        if world > 1:
+            t = ch.tensor([ms], dtype=ch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        others[name] = {'value': BATCH * world * args.steps / (ms * 1e-3), 'unit': 'images/s',
+                        'ms_per_step': ms / args.steps, 'h2d_bytes_per_step': h2d, 'source': describe(probe)}
+        del probe
     sampler = ClockSampler(local)
-    loader = make_loader(auto_pin)
+    loader = make_loader(None)
     exe = loader.graph.pipelines[0].executor
     ctx = exe.ctx
     e2e_ms, h2d_mean, launches_per_batch, digest = run_e2e(loader, sampler if rank == 0 else None)
-    if auto_pin:
-        pinned_ms, pinned_h2d, staged_ms, staged_h2d = e2e_ms, h2d_mean, other_ms, other_h2d
-    else:
-        pinned_ms, pinned_h2d, staged_ms, staged_h2d = other_ms, other_h2d, e2e_ms, h2d_mean
 
     # ------------------------------------------------------------------ inputs resident in HBM
     slots = loader.batches_ahead + 2
@@ -360,10 +378,10 @@ def main_ours(args):
     value_ms = v0.elapsed_time(v1)
     clocks = sampler.stop() if rank == 0 else None
 
-    times = ch.tensor([e2e_ms, value_ms, staged_ms, serial_ms, pinned_ms], dtype=ch.float64, device=device)
+    times = ch.tensor([e2e_ms, value_ms, serial_ms], dtype=ch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    e2e_ms, value_ms, staged_ms, serial_ms, pinned_ms = (float(v) for v in times.cpu())
+    e2e_ms, value_ms, serial_ms = (float(v) for v in times.cpu())
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -438,14 +456,8 @@ def main_ours(args):
                     'h2d_roofline': {'bound': 'host->device link', 'achieved': h2d_mean / (e2e_ms / args.steps * 1e-3) / 1e9,
                                      'peak': h2d_peak, 'unit': 'GB/s', 'frac': h2d_mean / (e2e_ms / args.steps * 1e-3) / 1e9 / h2d_peak,
                                      'note': 'per GPU, rank 0; peak = pinned 256 MB cudaMemcpy measured in this run'},
-                    'source': 'file pinned in host RAM, payloads gathered by the GPU over PCIe' if loader.memory_manager.pinned
-                    else 'file memory-mapped, staged by CPU threads'},
-            'e2e_staged': {'value': BATCH * world * args.steps / (staged_ms * 1e-3), 'unit': 'images/s',
-                           'ms_per_step': staged_ms / args.steps, 'h2d_bytes_per_step': staged_h2d,
-                           'source': 'Loader(pin_file=False): file memory-mapped, staged into pinned buffers by CPU threads'},
-            'e2e_pinned_file': {'value': BATCH * world * args.steps / (pinned_ms * 1e-3), 'unit': 'images/s',
-                                'ms_per_step': pinned_ms / args.steps, 'h2d_bytes_per_step': pinned_h2d,
-                                'source': 'Loader(pin_file=True): file in pinned host RAM, payloads gathered by the GPU'},
+                    'source': describe(loader)},
+            **others,
             'value_single_stream': {'value': BATCH * world * args.steps / (serial_ms * 1e-3), 'unit': 'images/s',
                                     'ms_per_step': serial_ms / args.steps},
             'gpu_launches': int(launches_per_batch * args.steps), 'roofline': roofline, 'cpu_baseline': cpu,

@@ -432,7 +432,29 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                 d.mcus_x = (uint16_t)((h.width + 8 * h.hs[0] - 1) / (8 * h.hs[0]));
                 d.mcus_y = (uint16_t)((h.height + 8 * h.vs[0] - 1) / (8 * h.vs[0]));
                 d.restart_interval = (uint16_t)h.restart_interval;
-                d.nblocks = (uint32_t)d.bpm * d.mcus_x * d.mcus_y;
+                d.mcu_rows = d.mcus_y;
+                d.idct_row0 = d.idct_col0 = 0;
+                d.idct_col1 = d.mcus_x;
+                // With a crop box only part of the image is needed.  The colour kernels of 4:2:0
+                // and 4:4:4 images convert the box alone and reach at most one chroma sample
+                // (two pixels, three with an odd edge) beyond it; other layouts convert the whole image.
+                const bool boxed = h.ncomp == 3 && ((h.hs[0] == 2 && h.vs[0] == 2 && (h.width + 1) / 2 >= 3) ||
+                                                    (h.hs[0] == 1 && h.vs[0] == 1));
+                if (plan->resize && boxed) {
+                    const int32_t *p = params + (size_t)i * n_params;
+                    if (p[0] >= 0 && p[2] > 0 && p[0] + p[2] <= (int)d.height && p[1] >= 0 && p[3] > 0 &&
+                        p[1] + p[3] <= (int)d.width) {
+                        const int mh = 8 * d.vs, mw = 8 * d.hs;
+                        const int y0 = p[0] - 3 < 0 ? 0 : p[0] - 3, x0 = p[1] - 3 < 0 ? 0 : p[1] - 3;
+                        const int y1 = p[0] + p[2] + 3 > (int)d.height ? (int)d.height : p[0] + p[2] + 3;
+                        const int x1 = p[1] + p[3] + 3 > (int)d.width ? (int)d.width : p[1] + p[3] + 3;
+                        d.idct_row0 = (uint16_t)(y0 / mh);
+                        d.mcu_rows = (uint16_t)((y1 - 1) / mh + 1);
+                        d.idct_col0 = (uint16_t)(x0 / mw);
+                        d.idct_col1 = (uint16_t)((x1 - 1) / mw + 1);
+                    }
+                }
+                d.nblocks = (uint32_t)d.bpm * d.mcus_x * d.mcu_rows;
             }
         } else {
             int r0 = 0, rows = d.height, c0 = 0, cols = d.width;
@@ -475,7 +497,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
             const double tc = s.staged_end > s.hdr.payload_off ? s.stage_ms[2] : 0.0;
             if (tg + tc > 0) ctx->share += 0.04 * ((double)tg - tc) / ((double)tg + tc);
             if (ctx->share < 0) ctx->share = 0;
-            if (ctx->share > 0.8) ctx->share = 0.8;
+            if (ctx->share > 0.5) ctx->share = 0.5;
         } else {
             cudaGetLastError(); // not run yet, or still running: keep the share
         }
@@ -539,6 +561,11 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         total_blocks += d.nblocks;
         d.clean_off = clean_bytes;
         clean_bytes += align_up((size_t)d.scan_len + 96, 16);
+        if (d.restart_interval) { // table of interval starts behind the clean stream
+            d.rst_off = clean_bytes;
+            const size_t mcus = (size_t)d.mcus_x * d.mcus_y;
+            clean_bytes += align_up(4 * ((mcus + d.restart_interval - 1) / d.restart_interval + 2), 16);
+        }
         for (int c = 0; c < h.ncomp; c++) {
             d.plane_off[c] = plane_bytes;
             const size_t pw = (size_t)d.mcus_x * (c == 0 ? d.hs : 1) * 8;

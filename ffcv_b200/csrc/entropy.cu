@@ -232,7 +232,18 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         if (carry_p >= total_bits || blk_base >= d.nblocks) break;
         const uint32_t first_sub = carry_p / S;
         // subsequences of this chunk that hold data; threads beyond them stay out of the repair
-        const uint32_t left = (total_bits - first_sub * S + S - 1) / S;
+        uint32_t left = (total_bits - first_sub * S + S - 1) / S;
+        // When the crop needs only the upper part of the image, so does the decoder: the bits still
+        // to decode are estimated from the blocks still missing (at the rate seen so far, or the
+        // stream's average for the first chunk) with a quarter to spare; a short estimate only
+        // costs another chunk.
+        if (d.mcu_rows < d.mcus_y) {
+            const uint64_t all_blocks = (uint64_t)d.bpm * d.mcus_x * d.mcus_y;
+            const uint64_t missing = d.nblocks - blk_base;
+            const uint64_t bits = blk_base ? missing * (carry_p + 1) / blk_base : missing * total_bits / all_blocks;
+            const uint64_t want = (bits + bits / 4 + (carry_p - first_sub * S)) / S + 2;
+            if (want < left) left = (uint32_t)want;
+        }
         const int nsub = left < (uint32_t)kEntropyThreads ? (int)left : kEntropyThreads;
         const bool active = tid < nsub;
         const uint32_t g = first_sub + tid;
@@ -304,7 +315,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
     __syncthreads();
 
     // ---- integrate the DC differences of each component over the scan
-    const int nmcu = d.mcus_x * d.mcus_y;
+    const int nmcu = d.mcus_x * d.mcu_rows; // the MCUs that were decoded
     int carry_y = 0, carry_cb = 0, carry_cr = 0;
     for (int base = 0; base < nmcu; base += kEntropyThreads) {
         const int m = base + tid;
@@ -339,118 +350,147 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
 }
 
 // ------------------------------------------------------------------------------------------
-// Sequential decoder, one thread per image: the general path for streams with restart markers
-// (DRI != 0), which the parallel kernel does not take.  Reads the stuffed stream directly.
+// Streams with restart markers (DRI != 0): every restart interval is an independent piece of the
+// stream (byte aligned, DC predictors reset, T.81 F.2.1.3.1 / E.2.4), so no speculation is
+// needed: the unstuffing pass also removes the RSTn markers and records where each interval
+// starts, then one thread decodes one interval straight into its blocks' final positions, DC
+// prediction included.  One CTA per image.
 
-struct ByteReader {
-    const uint8_t *p, *end;
-    uint32_t acc; // left-aligned
-    int n;
-    bool marker;
-};
-
-__device__ __forceinline__ void fill(ByteReader &r) {
-    while (r.n <= 24) {
-        uint32_t b = 0;
-        if (!r.marker && r.p < r.end) {
-            b = *r.p;
-            if (b == 0xFF) {
-                if (r.p + 1 < r.end && r.p[1] == 0) {
-                    r.p += 2;
-                } else {
-                    r.marker = true;
-                    b = 0;
-                }
-            } else {
-                r.p++;
-            }
+// Decodes `nblk` blocks starting at bit p (slot 0 of an MCU, predictors zero) into cf + blk * 64.
+// Returns the bit position reached, or 0xFFFFFFFF when the interval's bits ran out first.
+__device__ __forceinline__ uint32_t decode_interval(const uint32_t *__restrict__ words, uint32_t p, uint32_t limit,
+                                                    uint32_t nblk, int bpm, int luma, int ncomp,
+                                                    const HuffTable *s_tab, const uint8_t *s_zz,
+                                                    int16_t *__restrict__ cf, uint32_t blk) {
+    int pred[3] = {0, 0, 0};
+    int c = 0, z = 0;
+    int16_t *out = cf + (size_t)blk * 64;
+    uint32_t done = 0;
+    while (done < nblk) {
+        if (p >= limit) return 0xFFFFFFFFu;
+        const uint32_t w = peek32(words, p);
+        const bool dc = z == 0;
+        const int comp = (ncomp == 1 || c < luma) ? 0 : c - luma + 1;
+        const HuffTable &t = s_tab[2 * comp + (dc ? 0 : 1)];
+        int len, sym;
+        huff_lookup(t, w, len, sym);
+        const int s = sym & 15, r = sym >> 4;
+        const int zpos = dc ? 0 : z + r;
+        const int v = s ? extend((w << len) >> (32 - s), s) : 0;
+        if (dc) {
+            pred[comp] += v;
+            out[0] = (int16_t)pred[comp];
+        } else if (s != 0 && zpos < 64) {
+            out[s_zz[zpos]] = (int16_t)v;
         }
-        r.acc |= b << (24 - r.n);
-        r.n += 8;
+        const int zn = (dc | (s != 0)) ? zpos + 1 : (r == 15 ? z + 16 : 64);
+        p += len + s;
+        if (zn >= 64) {
+            z = 0;
+            done++;
+            out += 64;
+            c = (c + 1 == bpm) ? 0 : c + 1;
+        } else {
+            z = zn;
+        }
     }
+    return p;
 }
 
-__global__ void entropy_sequential_kernel(const ImageDesc *__restrict__ descs,
-                                          const int32_t *__restrict__ list, int n_list,
-                                          const uint8_t *__restrict__ blob,
-                                          const HuffTable *__restrict__ huff,
-                                          int16_t *__restrict__ coef, int32_t *__restrict__ status) {
-    const int li = blockIdx.x * blockDim.x + threadIdx.x;
-    if (li >= n_list) return;
-    const int img = list[li];
-    const ImageDesc &d = descs[img];
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
+entropy_restart_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
+                       const uint8_t *__restrict__ blob, const HuffTable *__restrict__ huff,
+                       uint8_t *__restrict__ clean, int16_t *__restrict__ coef, int32_t *__restrict__ status) {
+    __shared__ HuffTable s_tab[6];
+    __shared__ int s_warp[33];
+    __shared__ uint8_t s_zz[64];
+    __shared__ int s_bad;
+
+    const int img = list[blockIdx.x];
+    const ImageDesc d = descs[img];
+    const int tid = threadIdx.x;
     if (d.host_status != 0) {
-        status[img] = d.host_status;
+        if (tid == 0) status[img] = d.host_status;
         return;
     }
-    ByteReader r;
-    r.p = blob + d.payload_off + d.scan_off;
-    r.end = r.p + d.scan_len;
-    r.acc = 0;
-    r.n = 0;
-    r.marker = false;
-    int16_t *cf = coef + (size_t)d.block_base * 64;
-    const int luma = d.hs * d.vs, nmcu = d.mcus_x * d.mcus_y;
-    int pred[3] = {0, 0, 0};
-    int restarts_left = d.restart_interval;
-    uint32_t blk = 0;
-    int rc = 0;
-    for (int m = 0; m < nmcu && rc == 0; m++) {
-        if (d.restart_interval && restarts_left == 0) {
-            r.acc = 0;
-            r.n = 0;
-            r.marker = false;
-            while (r.p + 1 < r.end && !(r.p[0] == 0xFF && r.p[1] >= 0xD0 && r.p[1] <= 0xD7)) r.p++;
-            if (r.p + 1 >= r.end) {
-                rc = kErrData;
-                break;
-            }
-            r.p += 2;
-            pred[0] = pred[1] = pred[2] = 0;
-            restarts_left = d.restart_interval;
+    for (int c = 0; c < d.ncomp; c++) {
+        const uint32_t *sd = reinterpret_cast<const uint32_t *>(&huff[d.dc_tab[c]]);
+        const uint32_t *sa = reinterpret_cast<const uint32_t *>(&huff[d.ac_tab[c]]);
+        uint32_t *dd = reinterpret_cast<uint32_t *>(&s_tab[2 * c]);
+        uint32_t *da = reinterpret_cast<uint32_t *>(&s_tab[2 * c + 1]);
+        for (int i = tid; i < (int)(sizeof(HuffTable) / 4); i += kThreads) {
+            dd[i] = sd[i];
+            da[i] = sa[i];
         }
-        for (int c = 0; c < d.bpm; c++, blk++) {
-            const int comp = (d.ncomp == 1 || c < luma) ? 0 : c - luma + 1;
-            const HuffTable &dc = huff[d.dc_tab[comp]];
-            const HuffTable &ac = huff[d.ac_tab[comp]];
-            int len, sym;
-            fill(r);
-            huff_lookup(dc, r.acc, len, sym);
-            r.acc <<= len;
-            r.n -= len;
-            int s = sym & 15;
-            if (s) {
-                fill(r);
-                pred[comp] += extend(r.acc >> (32 - s), s);
-                r.acc <<= s;
-                r.n -= s;
-            }
-            cf[(size_t)blk * 64] = (int16_t)pred[comp];
-            for (int z = 1; z < 64;) {
-                fill(r);
-                huff_lookup(ac, r.acc, len, sym);
-                r.acc <<= len;
-                r.n -= len;
-                s = sym & 15;
-                const int run = sym >> 4;
-                if (s == 0) {
-                    if (run != 15) break;
-                    z += 16;
-                    continue;
-                }
-                z += run;
-                fill(r);
-                const int v = extend(r.acc >> (32 - s), s);
-                r.acc <<= s;
-                r.n -= s;
-                if (z > 63) break;
-                cf[(size_t)blk * 64 + kZigzagNatural[z]] = (int16_t)v;
-                z++;
-            }
-        }
-        if (d.restart_interval) restarts_left--;
     }
-    status[img] = rc;
+    if (tid < 64) s_zz[tid] = kZigzagNatural[tid];
+    if (tid == 0) s_bad = 0;
+
+    // ---- remove byte stuffing and restart markers; note where every interval starts
+    const uint8_t *scan = blob + d.payload_off + d.scan_off;
+    uint8_t *cl = clean + d.clean_off;
+    uint32_t *starts = reinterpret_cast<uint32_t *>(clean + d.rst_off); // byte offsets in the clean stream
+    const int nmcu_all = d.mcus_x * d.mcus_y, ri = d.restart_interval;
+    const uint32_t cap = (uint32_t)((nmcu_all + ri - 1) / ri) + 1; // entries the table holds
+    if (tid == 0) starts[0] = 0;
+    uint32_t clean_len = 0, n_mark = 0;
+    for (uint32_t base = 0; base < d.scan_len; base += kThreads * 16) {
+        const uint32_t my = base + tid * 16;
+        uint8_t b[17];
+        uint32_t keep = 0, marks = 0;
+        int prev = (my > 0 && my <= d.scan_len) ? scan[my - 1] : 0;
+#pragma unroll
+        for (int i = 0; i < 17; i++) b[i] = my + i < d.scan_len ? scan[my + i] : 0;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const uint32_t at = my + i;
+            const bool rst_ff = b[i] == 0xFF && (b[i + 1] & 0xF8) == 0xD0;
+            const bool rst_code = prev == 0xFF && (b[i] & 0xF8) == 0xD0;
+            const bool stuffing = b[i] == 0 && prev == 0xFF;
+            if (at < d.scan_len && !rst_ff && !rst_code && !stuffing) keep |= 1u << i;
+            if (at < d.scan_len && rst_code) marks |= 1u << i;
+            prev = b[i];
+        }
+        int total, mtotal;
+        const int off = block_scan_exclusive(__popc(keep), s_warp, total);
+        const int moff = block_scan_exclusive(__popc(marks), s_warp, mtotal);
+        uint32_t o = clean_len + off, m = n_mark + moff;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            if (keep & (1u << i)) cl[(o++) ^ 3u] = b[i];
+            if (marks & (1u << i)) {
+                m++;
+                if (m < cap) starts[m] = o; // interval m begins with the next byte kept
+            }
+        }
+        clean_len += total;
+        n_mark += mtotal;
+    }
+    if (tid < 64) cl[(clean_len + tid) ^ 3u] = 0;
+    __syncthreads();
+
+    // ---- one thread per restart interval
+    const uint32_t *words = reinterpret_cast<const uint32_t *>(cl);
+    const int bpm = d.bpm, luma = d.hs * d.vs, ncomp = d.ncomp;
+    const int nmcu = d.mcus_x * d.mcu_rows; // the crop may need only the upper rows
+    const uint32_t needed = (uint32_t)((nmcu + ri - 1) / ri);
+    const uint32_t found = n_mark + 1 < cap ? n_mark + 1 : cap;
+    int16_t *cf = coef + (size_t)d.block_base * 64;
+    if (found < needed) {
+        if (tid == 0) s_bad = 1; // fewer intervals than the frame needs
+    }
+    for (uint32_t k = tid; k < needed && k < found; k += kThreads) {
+        const int first = (int)k * ri;
+        const int count = nmcu - first < ri ? nmcu - first : ri;
+        const uint32_t p0 = starts[k] * 8;
+        const uint32_t limit = (k + 1 < found ? starts[k + 1] : clean_len) * 8;
+        const uint32_t p = decode_interval(words, p0, limit, (uint32_t)count * bpm, bpm, luma, ncomp, s_tab, s_zz, cf,
+                                           (uint32_t)first * bpm);
+        if (p == 0xFFFFFFFFu) s_bad = 1;
+    }
+    __syncthreads();
+    if (tid == 0) status[img] = s_bad ? kErrData : 0;
 }
 
 void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
@@ -471,8 +511,7 @@ void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_li
         }
     }
     if (n_seq > 0)
-        entropy_sequential_kernel<<<(n_seq + 31) / 32, 32, 0, stream>>>(descs, seq_list, n_seq, blob,
-                                                                        huff, coef, status);
+        entropy_restart_kernel<256><<<n_seq, 256, 0, stream>>>(descs, seq_list, blob, huff, clean, coef, status);
 }
 
 } // namespace ffcvb

@@ -69,6 +69,7 @@ idct_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ lis
     const uint32_t mcu = b / d.bpm;
     const int slot = (int)(b - mcu * d.bpm);
     const int my = mcu / d.mcus_x, mx = mcu - my * d.mcus_x;
+    if (my < d.idct_row0 || mx < d.idct_col0 || mx >= d.idct_col1) return; // outside the crop's reach
     int comp, bx, by, plane_w;
     if (d.ncomp == 1 || slot < luma) {
         comp = 0;

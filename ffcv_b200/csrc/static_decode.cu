@@ -104,7 +104,16 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     d.mcus_x = (uint16_t)((h.width + 8 * h.hs[0] - 1) / (8 * h.hs[0]));
     d.mcus_y = (uint16_t)((h.height + 8 * h.vs[0] - 1) / (8 * h.vs[0]));
     d.restart_interval = (uint16_t)h.restart_interval;
+    d.mcu_rows = d.mcus_y;
+    d.idct_row0 = d.idct_col0 = 0;
+    d.idct_col1 = d.mcus_x;
     d.nblocks = (uint32_t)d.bpm * d.mcus_x * d.mcus_y;
+    if (d.restart_interval) { // table of restart-interval starts behind the clean stream
+        d.rst_off = ((size_t)d.scan_len + 96 + 15) & ~(size_t)15;
+        const size_t mcus = (size_t)d.mcus_x * d.mcus_y;
+        if (d.rst_off + 4 * ((mcus + d.restart_interval - 1) / d.restart_interval + 2) > kCleanBytes)
+            return reject(FFCVB_E_LIMIT, "stream with restart markers too large for the static scratch");
+    }
     const size_t luma_samples = (size_t)d.mcus_x * d.hs * 8 * d.mcus_y * d.vs * 8;
     if (height > 65535 || width > 65535 || luma_samples > kMaxPaddedSamples)
         return reject(FFCVB_E_LIMIT, "image larger than FFCVB_STATIC_MAX_PADDED_PIXELS");

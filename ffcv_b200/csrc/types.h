@@ -29,9 +29,16 @@ struct ImageDesc {
     uint8_t dc_tab[kMaxComponents], ac_tab[kMaxComponents]; // indices into the batch's HuffTable array
     uint8_t q_tab[kMaxComponents];                          // indices into the batch's MultTable array
     uint8_t pad0;
-    uint32_t nblocks;      // 8x8 blocks in the scan
+    // The crop box decides how much of the image is needed: the entropy decoder stops after
+    // `mcu_rows` rows of MCUs and the inverse transform runs only on the MCUs of the box below
+    // (the crop box grown by the reach of the chroma filter).  Whole image when there is no crop.
+    uint16_t mcu_rows;                           // MCU rows to entropy-decode (<= mcus_y)
+    uint16_t idct_row0, idct_col0, idct_col1;    // MCU box to transform: rows [idct_row0, mcu_rows), cols [idct_col0, idct_col1)
+    uint32_t nblocks;      // 8x8 blocks to decode: bpm * mcus_x * mcu_rows
     uint32_t block_base;   // first block of this image in the batch coefficient buffer
     uint64_t clean_off;    // byte offset of the unstuffed scan in the bitstream scratch (4-aligned)
+    uint64_t rst_off;      // streams with restart markers: byte offset, in the same scratch, of a table of
+                           // ceil(MCUs / restart_interval) + 1 uint32 interval starts (4-aligned)
     uint64_t plane_off[kMaxComponents]; // byte offsets of the Y/Cb/Cr planes in the plane scratch
     uint64_t rgb_off;      // byte offset of the decoded h*w*3 image in the RGB scratch
     uint64_t src_addr;     // device-visible address of the payload in pinned host memory (0: staged copy)

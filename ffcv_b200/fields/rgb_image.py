@@ -23,11 +23,15 @@ from .base import ARG_TYPE, Field
 IMAGE_MODES = {'jpg': 0, 'raw': 1}
 
 
-def encode_jpeg(numpy_image, quality):
+def encode_jpeg(numpy_image, quality, restart_interval=0):
     """``cv2.imencode('.jpg', BGR, [IMWRITE_JPEG_QUALITY, q])`` as rgb_image.py:26-34 does:
-    baseline, 4:2:0, standard Huffman tables, no restart markers."""
+    baseline, 4:2:0, standard Huffman tables, no restart markers -- unless ``restart_interval``
+    (in MCUs) asks for them."""
     bgr = cv2.cvtColor(numpy_image, cv2.COLOR_RGB2BGR)
-    ok, result = cv2.imencode('.jpg', bgr, [int(cv2.IMWRITE_JPEG_QUALITY), quality])
+    flags = [int(cv2.IMWRITE_JPEG_QUALITY), quality]
+    if restart_interval:
+        flags += [int(cv2.IMWRITE_JPEG_RST_INTERVAL), int(restart_interval)]
+    ok, result = cv2.imencode('.jpg', bgr, flags)
     if not ok:
         raise ValueError("Impossible to encode image in jpeg")
     return result.reshape(-1)
@@ -171,15 +175,23 @@ class RGBImageField(Field):
 
     ``write_mode`` is 'raw', 'jpg', 'smart' or 'proportion'; ``max_resolution`` bounds the longer
     side at write time; ``jpeg_quality`` and ``compress_probability`` as in the reference.
+
+    ``jpeg_restart_interval`` (not in the reference; a write-time choice that is not stored in the
+    field's arguments) makes the encoder emit a restart marker every that many MCUs.  The file
+    stays an ordinary ``.beton`` that the reference reads as well (restart markers are part of
+    baseline JPEG); here such streams need no speculative decoding: every interval is decoded by
+    its own GPU thread.  4 to 8 MCUs cost about 1 % of file size.
     """
 
     def __init__(self, write_mode='raw', max_resolution: int = None, smart_threshold: int = None,
-                 jpeg_quality: int = 90, compress_probability: float = 0.5) -> None:
+                 jpeg_quality: int = 90, compress_probability: float = 0.5,
+                 jpeg_restart_interval: int = 0) -> None:
         self.write_mode = write_mode
         self.smart_threshold = smart_threshold
         self.max_resolution = max_resolution
         self.jpeg_quality = int(jpeg_quality)
         self.proportion = compress_probability
+        self.jpeg_restart_interval = int(jpeg_restart_interval)
 
     @property
     def metadata_type(self) -> np.dtype:
@@ -196,7 +208,7 @@ class RGBImageField(Field):
         return np.zeros(1, dtype=ARG_TYPE)[0]
 
     def encode_jpeg(self, image):
-        return encode_jpeg(image, self.jpeg_quality)
+        return encode_jpeg(image, self.jpeg_quality, self.jpeg_restart_interval)
 
     def choose_mode(self, image):
         """Returns ('jpg' | 'raw', jpeg bytes or None)."""

@@ -95,9 +95,11 @@ def _field_444_class():
 
         def encode_jpeg(self, image):
             import cv2
-            ok, res = cv2.imencode('.jpg', cv2.cvtColor(image, cv2.COLOR_RGB2BGR),
-                                   [int(cv2.IMWRITE_JPEG_QUALITY), self.jpeg_quality,
-                                    int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR), int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444)])
+            flags = [int(cv2.IMWRITE_JPEG_QUALITY), self.jpeg_quality,
+                     int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR), int(cv2.IMWRITE_JPEG_SAMPLING_FACTOR_444)]
+            if self.jpeg_restart_interval:
+                flags += [int(cv2.IMWRITE_JPEG_RST_INTERVAL), self.jpeg_restart_interval]
+            ok, res = cv2.imencode('.jpg', cv2.cvtColor(image, cv2.COLOR_RGB2BGR), flags)
             if not ok:
                 raise ValueError("Impossible to encode image in jpeg")
             return res.reshape(-1)
@@ -107,7 +109,7 @@ def _field_444_class():
 RGBImageField444 = None
 
 
-def make_field(cfg_id):
+def make_field(cfg_id, restart_interval=0):
     from .fields import RGBImageField
     global RGBImageField444
     cfg = CONFIGS[cfg_id]
@@ -115,18 +117,19 @@ def make_field(cfg_id):
         if RGBImageField444 is None:
             RGBImageField444 = _field_444_class()
             RGBImageField444.__qualname__ = 'RGBImageField444'  # picklable by module attribute
-        return RGBImageField444(**cfg['field'])
-    return RGBImageField(**cfg['field'])
+        return RGBImageField444(**cfg['field'], jpeg_restart_interval=restart_interval)
+    return RGBImageField(**cfg['field'], jpeg_restart_interval=restart_interval)
 
 
-def write_dataset(cfg_id, path, count=None, num_workers=-1, page_size=None):
-    """Writes ``count`` samples (default: the configuration's full size) of a configuration."""
+def write_dataset(cfg_id, path, count=None, num_workers=-1, page_size=None, restart_interval=0):
+    """Writes ``count`` samples (default: the configuration's full size) of a configuration;
+    ``restart_interval`` > 0 writes the JPEG samples with a restart marker every that many MCUs."""
     from .fields import IntField
     from .writer import DatasetWriter
     kwargs = {} if page_size is None else {'page_size': page_size}
     if cfg_id == 4 and page_size is None:
         kwargs['page_size'] = 1 << 25  # 4:4:4 q95 images of ~2-4 MB: 32 MiB pages waste less
-    writer = DatasetWriter(path, {'image': make_field(cfg_id), 'label': IntField()},
+    writer = DatasetWriter(path, {'image': make_field(cfg_id, restart_interval), 'label': IntField()},
                            num_workers=num_workers, **kwargs)
     writer.from_indexed_dataset(SyntheticImageDataset(cfg_id, count), chunksize=16)
     return path

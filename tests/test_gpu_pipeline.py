@@ -94,6 +94,25 @@ def test_config2_fullres_mix_rrc224(datasets, pin_file, share):
     compare_epoch(loader)
 
 
+@pytest.mark.parametrize('cfg,interval,res', [(2, 4, 224), (1, 1, 160), (2, 25, 224), (4, 8, 384)])
+def test_streams_with_restart_markers(tmp_path, cfg, interval, res):
+    """Datasets written with the restart-interval option: every interval is decoded by its own
+    thread (no speculation); the pixels must be those of the oracle, crop-limited decode included."""
+    from ffcv_b200 import OrderOption
+    from ffcv_b200.fields.decoders import RandomResizedCropRGBImageDecoder, SimpleRGBImageDecoder
+    from ffcv_b200.synthetic import write_dataset
+    from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, ToTorchImage
+    n = 6 if cfg == 4 else 64
+    path = write_dataset(cfg, str(tmp_path / f'c{cfg}_rst{interval}.beton'), n, num_workers=4, restart_interval=interval)
+    pipes = {'image': [RandomResizedCropRGBImageDecoder((res, res)), RandomHorizontalFlip(),
+                       NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()],
+             'label': None}
+    loader = _loader(path, min(n, 32), pipes, order=OrderOption.QUASI_RANDOM)
+    exe = image_executor(loader)
+    compare_epoch(loader)
+    assert exe.ctx.launches(0) >= 4
+
+
 def test_config3_center_crop_validation(datasets):
     from ffcv_b200.fields.decoders import CenterCropRGBImageDecoder
     from ffcv_b200.transforms import NormalizeImage, ToDevice, ToTensor, ToTorchImage
