@@ -59,6 +59,8 @@ def parse_args():
     ap.add_argument('--images', type=int, default=4096, help='distinct images in the synthetic dataset')
     ap.add_argument('--workers', type=int, default=0, help='host staging threads per rank (0: cores / ranks)')
     ap.add_argument('--batches-ahead', type=int, default=3)
+    ap.add_argument('--restart-interval', type=int, default=0,
+                    help='write the JPEG samples with a restart marker every N MCUs (0: as the reference writes them)')
     ap.add_argument('--no-cpu-baseline', action='store_true', help='skip the CPU oracle leg (profiling runs)')
     return ap.parse_args()
 
@@ -68,18 +70,19 @@ def rank_info():
             int(os.environ.get('WORLD_SIZE', 1)))
 
 
-def dataset_path(images):
+def dataset_path(images, restart_interval=0):
     base = '/dev/shm' if os.path.isdir('/dev/shm') and os.access('/dev/shm', os.W_OK) else tempfile.gettempdir()
-    return os.path.join(base, f'ffcv_b200_bench_c{CFG}_{images}_of_{EPOCH_SAMPLES}.beton')
+    tag = f'_rst{restart_interval}' if restart_interval else ''
+    return os.path.join(base, f'ffcv_b200_bench_c{CFG}_{images}_of_{EPOCH_SAMPLES}{tag}.beton')
 
 
-def ensure_dataset(images):
+def ensure_dataset(images, restart_interval=0):
     """Written once (rank 0) before any timing; other ranks wait for the barrier that follows."""
     from ffcv_b200.synthetic import replicate_samples, write_dataset
-    path = dataset_path(images)
+    path = dataset_path(images, restart_interval)
     if not os.path.exists(path):
         tmp = path + f'.tmp{os.getpid()}'
-        write_dataset(CFG, tmp, images, num_workers=len(os.sched_getaffinity(0)))
+        write_dataset(CFG, tmp, images, num_workers=len(os.sched_getaffinity(0)), restart_interval=restart_interval)
         # the configuration's epoch length (200,000 samples) over the bounded set of distinct images
         replicate_samples(tmp, EPOCH_SAMPLES)
         os.replace(tmp, path)
@@ -193,14 +196,17 @@ def run_oracle(batches, threads):
     return times
 
 
-def config_dict(world, images, workers):
-    return {'workload': 'config 2: proportion(0.5) JPEG q90 4:2:0 / raw, short side 300-500, max side 500 -> '
+def config_dict(world, images, workers, restart_interval=0):
+    cfg = {'workload': 'config 2: proportion(0.5) JPEG q90 4:2:0 / raw, short side 300-500, max side 500 -> '
                         'RRC-224 + flip + fp16 normalise, channels-last',
             'batch_per_gpu': BATCH, 'global_batch': BATCH * world, 'dataset_samples': EPOCH_SAMPLES,
             'distinct_images': images,
             'order': 'QUASI_RANDOM', 'sharding': 'index sharding, no collective' if world > 1 else 'single GPU',
             'host_threads_per_rank': workers,
             'l2': 'inputs larger than L2: consecutive steps read different batches (5 slots x ~100 MB)'}
+    if restart_interval:
+        cfg['jpeg_restart_interval'] = restart_interval  # not the reference's file format default
+    return cfg
 
 
 def main_reference(args):
@@ -208,7 +214,7 @@ def main_reference(args):
     rank, _, world = rank_info()
     if rank != 0:
         return
-    path = ensure_dataset(args.images * min(world, 4))
+    path = ensure_dataset(args.images * min(world, 4), args.restart_interval)
     threads = len(os.sched_getaffinity(0))
     n = args.steps + args.warmup
     batches = oracle_batches(path, 0, min(n, 8))
@@ -220,7 +226,7 @@ def main_reference(args):
     line = {'impl': 'reference', 'metric': 'RRC-224 decode+augment images/s', 'value': value, 'unit': 'images/s',
             'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 * total / args.steps,
             'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'u8', 'data': 'synthetic',
-            'config': config_dict(world, args.images * min(world, 4), threads),
+            'config': config_dict(world, args.images * min(world, 4), threads, args.restart_interval),
             'cpu_baseline': {'value': value, 'unit': 'images/s', 'cores': threads, 'kind': 'port',
                              'sample': f'{args.steps} batches of {BATCH} images of the workload'},
             'e2e': {'value': value, 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
@@ -246,9 +252,9 @@ def main_ours(args):
 
     images = args.images * min(world, 4)
     if rank == 0:
-        ensure_dataset(images)
+        ensure_dataset(images, args.restart_interval)
     barrier()
-    path = dataset_path(images)
+    path = dataset_path(images, args.restart_interval)
     cores = len(os.sched_getaffinity(0))
     workers = args.workers or max(2, cores // max(1, world))
 
@@ -449,7 +455,7 @@ def main_ours(args):
     line = {'metric': 'RRC-224 decode+augment images/s', 'value': BATCH * world * args.steps / (value_ms * 1e-3),
             'unit': 'images/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': value_ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
-            'dtype': 'u8', 'data': 'synthetic', 'config': config_dict(world, images, workers),
+            'dtype': 'u8', 'data': 'synthetic', 'config': config_dict(world, images, workers, args.restart_interval),
             'e2e': {'value': BATCH * world * args.steps / (e2e_ms * 1e-3), 'unit': 'images/s',
                     'ms_per_step': e2e_ms / args.steps, 'h2d_bytes_per_step': h2d_mean,
                     'd2h_bytes_per_step': 8,

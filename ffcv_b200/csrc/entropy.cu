@@ -155,7 +155,12 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
     return done;
 }
 
-template <int kEntropyThreads>
+// kStaged: the chunk's bits are copied to shared memory first (subsequences of up to 1280 bits);
+// otherwise the threads read the unstuffed stream in global memory, which allows subsequences of
+// any length: a multi-megabit image is then one chunk of kEntropyThreads long subsequences that
+// re-synchronise in two or three (long, fully parallel) rounds instead of dozens of chunks that
+// wait for one another.
+template <int kEntropyThreads, bool kStaged>
 __global__ void __launch_bounds__(kEntropyThreads)
 entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
                         const uint8_t *__restrict__ blob, const HuffTable *__restrict__ huff,
@@ -253,8 +258,9 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         // The chunk's bits go to shared memory: every lane of a warp reads a different part of the
         // stream for every symbol, which shared memory serves at a few cycles per warp while the
         // same pattern on global memory saturates the L1 tag stage (one sector lookup per cycle).
-        const uint32_t bit_base = first_sub * S; // S is a multiple of 128: 16-byte aligned in the stream
-        {
+        const uint32_t bit_base = kStaged ? first_sub * S : 0; // S is a multiple of 128: 16-byte aligned in the stream
+        const uint32_t *stream = kStaged ? s_stream : words;
+        if (kStaged) {
             uint32_t n16 = ((uint32_t)nsub * S + 127) / 128 + 1; // one vector of overrun for the last symbol
             const uint32_t have16 = (clean_len + 64 - (bit_base >> 3)) / 16; // zero padding included
             if (n16 > have16) n16 = have16;
@@ -290,7 +296,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
                 Cursor cur = unpack(in);
                 uint32_t t_end = (first_sub + (uint32_t)t + 1) * S;
                 if (t_end > total_bits) t_end = total_bits;
-                s_blocks[t] = (uint16_t)decode_span<false>(s_stream, bit_base, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
+                s_blocks[t] = (uint16_t)decode_span<false>(stream, bit_base, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
                 const unsigned long long out = pack(cur);
                 if (s_state[t + 1] != out) { // only this thread writes entry t + 1 in this round
                     s_state[t + 1] = out;
@@ -304,7 +310,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         const int first = block_scan_exclusive(my_blocks, s_warp, chunk_blocks);
         if (active) {
             Cursor cur = unpack(s_state[tid]);
-            decode_span<true>(s_stream, bit_base, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
+            decode_span<true>(stream, bit_base, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
                               blk_base + (uint32_t)first, d.nblocks);
         }
         carry = s_state[nsub];
@@ -498,16 +504,24 @@ void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_li
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
                            int subseq_bits, int entropy_threads, cudaStream_t stream) {
     if (n_list > 0) {
+        const bool staged = subseq_bits <= kMaxStagedBits;
         auto launch = [&](auto kernel, int threads) {
-            const size_t smem = ((size_t)threads * subseq_bits / 8 + 63) / 16 * 16 + 16;
+            const size_t smem = staged ? ((size_t)threads * subseq_bits / 8 + 63) / 16 * 16 + 16 : 16;
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             kernel<<<n_list, threads, smem, stream>>>(descs, list, blob, huff, clean, coef, status, subseq_bits);
         };
         switch (entropy_threads) {
-        case 128: launch(entropy_parallel_kernel<128>, 128); break;
-        case 256: launch(entropy_parallel_kernel<256>, 256); break;
-        case 1024: launch(entropy_parallel_kernel<1024>, 1024); break;
-        default: launch(entropy_parallel_kernel<512>, 512);
+        case 128:
+            if (staged) launch(entropy_parallel_kernel<128, true>, 128); else launch(entropy_parallel_kernel<128, false>, 128);
+            break;
+        case 256:
+            if (staged) launch(entropy_parallel_kernel<256, true>, 256); else launch(entropy_parallel_kernel<256, false>, 256);
+            break;
+        case 1024:
+            if (staged) launch(entropy_parallel_kernel<1024, true>, 1024); else launch(entropy_parallel_kernel<1024, false>, 1024);
+            break;
+        default:
+            if (staged) launch(entropy_parallel_kernel<512, true>, 512); else launch(entropy_parallel_kernel<512, false>, 512);
         }
     }
     if (n_seq > 0)

@@ -11,6 +11,9 @@ namespace ffcvb {
 // PCIe) into its place in the device blob.  Source and destination share their alignment mod 16.
 void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, cudaStream_t stream);
 
+// Longest subsequence whose chunk the entropy decoder stages in shared memory.
+constexpr int kMaxStagedBits = 1280;
+
 // Entropy decode of every JPEG sample listed in `list` (indices into descs): unstuffs the scan
 // into `clean`, Huffman-decodes it into quantised coefficients (natural order inside a block,
 // blocks in scan order, DC un-differenced) in `coef`, and records a per-sample status.
