@@ -586,8 +586,21 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         d.rgb_off = rgb_bytes;
         rgb_bytes += align_up((size_t)d.height * d.width * 3, 16);
         if ((int)d.height * d.width > max_pixels) max_pixels = (int)d.height * d.width;
-        if (d.width > max_w) max_w = d.width;
-        if (d.height > max_h) max_h = d.height;
+        {   // extent the colour kernels' grids must cover: the crop box (plus the odd edge of a
+            // chroma cell) where the kernel converts only that, else the whole image
+            int bw = d.width, bh = d.height;
+            const bool boxed = d.ncomp == 3 && ((d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3) || (d.hs == 1 && d.vs == 1));
+            if (plan->resize && boxed) {
+                const int32_t *p = params + (size_t)i * n_params;
+                if (p[0] >= 0 && p[2] > 0 && p[0] + p[2] <= (int)d.height && p[1] >= 0 && p[3] > 0 &&
+                    p[1] + p[3] <= (int)d.width) {
+                    bw = p[3] + 2 < bw ? p[3] + 2 : bw;
+                    bh = p[2] + 2 < bh ? p[2] + 2 : bh;
+                }
+            }
+            if (bw > max_w) max_w = bw;
+            if (bh > max_h) max_h = bh;
+        }
         if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3)
             n_quad++;
         else if (d.ncomp == 3 && d.hs == 1 && d.vs == 1)
@@ -632,11 +645,22 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     }
     s.staged_end = off;
     for (int i = 0; i < n; i++) {
-        if (descs[i].src_addr == 0) continue;
-        // gathered payloads keep their source alignment mod 16 so both sides move in 16-byte words
-        const bool rowwise = descs[i].mode == FFCVB_MODE_RAW && descs[i].cols != descs[i].width;
-        descs[i].payload_off = off + (rowwise ? 0 : (descs[i].src_addr & 15));
-        off = align_up(descs[i].payload_off + descs[i].payload_size, kPayloadAlign);
+        ImageDesc &d = descs[i];
+        if (d.src_addr == 0) continue;
+        // Gathered payloads keep their source alignment mod 16 so that both sides move in whole
+        // 16-byte words.  A crop box is fetched row by row: every row gets a 16-byte aligned slot
+        // wide enough for the aligned words that contain it, and its pixels start inside the slot
+        // at the row's own source alignment (ImageDesc::raw_skew tells the reader).
+        const bool rowwise = d.mode == FFCVB_MODE_RAW && d.cols != d.width;
+        if (rowwise) {
+            d.raw_pitch = (uint32_t)align_up((size_t)d.cols * 3 + 15, 16);
+            d.payload_size = (uint32_t)((size_t)d.rows * d.raw_pitch);
+            d.raw_skew = 1;
+            d.payload_off = off;
+        } else {
+            d.payload_off = off + (d.src_addr & 15);
+        }
+        off = align_up(d.payload_off + d.payload_size, kPayloadAlign);
     }
     hd.total_bytes = off;
 

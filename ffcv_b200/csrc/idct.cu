@@ -157,37 +157,45 @@ gather_payloads_kernel(const ImageDesc *__restrict__ descs, int n, uint8_t *__re
         if (d.src_addr == 0 || d.payload_size == 0) continue;
         const uint8_t *src = reinterpret_cast<const uint8_t *>(d.src_addr);
         uint8_t *dst = blob + d.payload_off;
-        if (d.mode == 1 && d.cols != d.width) {
-            // Raw sample, crop box only: one warp per row.  The row's bytes are fetched as the
-            // 16-byte chunks of host memory that contain them (all of a row's requests are issued
-            // before the first store) and land tightly packed in the blob.
+        if (d.mode == 1 && d.raw_skew) {
+            // Raw sample, crop box only.  A row is fetched as the aligned 16-byte words of host
+            // memory that contain it and stored as such into its 16-byte aligned slot, so the
+            // pixels keep their source alignment inside the slot and no byte is shuffled.  (A
+            // word that holds one byte of the row lies in the same page as that byte: the reads
+            // stay inside the pinned allocation.)  Two rows per warp and pass, all loads of a
+            // pass issued before its stores: up to 8 x 512 bytes in flight per warp.
             const uint32_t run = (uint32_t)d.cols * 3, pitch = (uint32_t)d.width * 3;
-            for (int r = warp; r < d.rows; r += nwarps) {
-                const uint8_t *s = src + (size_t)r * pitch;
-                uint8_t *o = dst + (size_t)r * d.raw_pitch;
-                const uint32_t a = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
-                const uint4 *s16 = reinterpret_cast<const uint4 *>(s - a);
-                const uint32_t nchunk = (a + run + 15) >> 4;
-                uint4 v[4];
+            for (int r0 = 2 * warp; r0 < d.rows; r0 += 2 * nwarps) {
+                const uint4 *s16[2];
+                uint4 *d16[2];
+                uint32_t nchunk[2];
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    const int r = r0 + q;
+                    const uint8_t *s = src + (size_t)r * pitch;
+                    const uint32_t a = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
+                    s16[q] = reinterpret_cast<const uint4 *>(s - a);
+                    d16[q] = reinterpret_cast<uint4 *>(dst + (size_t)r * d.raw_pitch);
+                    nchunk[q] = r < d.rows ? (a + run + 15) >> 4 : 0;
+                }
+                const uint32_t most = nchunk[0] > nchunk[1] ? nchunk[0] : nchunk[1];
 #pragma unroll 1
-                for (uint32_t c0 = 0; c0 < nchunk; c0 += 128) {
+                for (uint32_t c0 = 0; c0 < most; c0 += 128) {
+                    uint4 v[2][4];
 #pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const uint32_t c = c0 + u * 32 + lane;
-                        if (c < nchunk) v[u] = s16[c];
-                    }
+                    for (int q = 0; q < 2; q++)
 #pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const uint32_t c = c0 + u * 32 + lane;
-                        if (c >= nchunk) continue;
-                        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                        const int base = (int)(c << 4) - (int)a;
-#pragma unroll
-                        for (int b = 0; b < 16; b++) {
-                            const int k = base + b;
-                            if (k >= 0 && k < (int)run) o[k] = (uint8_t)(w[b >> 2] >> (8 * (b & 3)));
+                        for (int u = 0; u < 4; u++) {
+                            const uint32_t c = c0 + u * 32 + lane;
+                            if (c < nchunk[q]) v[q][u] = s16[q][c];
                         }
-                    }
+#pragma unroll
+                    for (int q = 0; q < 2; q++)
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const uint32_t c = c0 + u * 32 + lane;
+                            if (c < nchunk[q]) d16[q][c] = v[q][u];
+                        }
                 }
             }
             continue;

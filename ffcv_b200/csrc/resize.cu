@@ -132,6 +132,9 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     // ---- where the sample's pixels are
     const uint8_t *base;
     int stride, row0 = 0, col0 = 0, img_h, img_w;
+    // rows of a gathered crop box start at their source alignment inside their slot (raw_skew)
+    uint32_t skew_base = 0, skew_pitch = 0;
+    bool skew = false;
     bool ok = true;
     if (src.descs) {
         const ImageDesc &d = src.descs[i];
@@ -144,6 +147,11 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
             col0 = d.col0;
             stride = (int)d.raw_pitch;
             ok = d.host_status == 0;
+            if (d.raw_skew) {
+                skew = true;
+                skew_base = (uint32_t)(d.src_addr & 15);
+                skew_pitch = (uint32_t)d.width * 3;
+            }
         } else {
             base = src.rgb + d.rgb_off;
             ok = d.host_status == 0 && (status == nullptr || status[i] == 0);
@@ -187,7 +195,13 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     }
     __syncthreads();
 
-    const uint8_t *roi = base + (ptrdiff_t)(ci - row0) * stride + (cj - col0) * 3;
+    const int roff = ci - row0, coff = (cj - col0) * 3;
+    auto row_ptr = [&](int y) -> const uint8_t * { // first pixel of row y of the crop
+        const int rr = roff + y;
+        const uint8_t *p = base + (ptrdiff_t)rr * stride + coff;
+        if (skew) p += (skew_base + (uint32_t)rr * skew_pitch) & 15u;
+        return p;
+    };
     const int npix = rows * out_w;
     const uint32_t inv_w = (uint32_t)((0x100000000ull + out_w - 1) / out_w); // pix / out_w for pix < 2^16
     for (int pix = threadIdx.x; pix < npix; pix += blockDim.x) {
@@ -216,14 +230,14 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
         }
         if (!filled && ok) {
             if (regime == kCopy) {
-                const uint8_t *p = roi + (size_t)y * stride + x * 3;
+                const uint8_t *p = row_ptr(y) + x * 3;
                 val[0] = p[0];
                 val[1] = p[1];
                 val[2] = p[2];
             } else if (regime == kInteger) {
                 int s0 = 0, s1 = 0, s2 = 0;
                 for (int j = 0; j < isy; j++) {
-                    const uint8_t *p = roi + (size_t)(y * isy + j) * stride + (x * isx) * 3;
+                    const uint8_t *p = row_ptr(y * isy + j) + (x * isx) * 3;
                     for (int k = 0; k < isx; k++, p += 3) {
                         s0 += p[0];
                         s1 += p[1];
@@ -249,9 +263,11 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
                 const bool yl = yc & (1 << 16), yr = yc & (1 << 17);
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f;
                 for (int j = 0; j < yn; j++) {
-                    const uint8_t *p = roi + (size_t)(yf + j) * stride + xf * 3;
+                    const uint8_t *p = row_ptr(yf + j) + xf * 3;
                     float r0 = 0.f, r1 = 0.f, r2 = 0.f;
                     for (int k = 0; k < xn; k++, p += 3) {
+                        // (three separate loops for the left, whole and right cells measured slower:
+                        // the lanes of a warp disagree on which cells they have)
                         const float w = (k == 0 && xl) ? xwl : ((k == xn - 1 && xr) ? xwr : xwm);
                         r0 = __fadd_rn(r0, __fmul_rn(u8f(p[0]), w));
                         r1 = __fadd_rn(r1, __fmul_rn(u8f(p[1]), w));
@@ -276,7 +292,7 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
                 const int sy = ty.first[y], yw = ty.count[y], b0 = yw >> 16, b1 = yw & 0xffff;
                 const int sx1 = min(sx + 1, cw - 1);
                 const int ry0 = min(sy, ch - 1), ry1 = min(sy + 1, ch - 1);
-                const uint8_t *S0 = roi + (size_t)ry0 * stride, *S1 = roi + (size_t)ry1 * stride;
+                const uint8_t *S0 = row_ptr(ry0), *S1 = row_ptr(ry1);
 #pragma unroll
                 for (int c = 0; c < 3; c++) {
                     const int h0 = S0[3 * sx + c] * xa0 + S0[3 * sx1 + c] * xa1;

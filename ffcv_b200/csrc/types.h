@@ -28,7 +28,8 @@ struct ImageDesc {
     uint16_t restart_interval;
     uint8_t dc_tab[kMaxComponents], ac_tab[kMaxComponents]; // indices into the batch's HuffTable array
     uint8_t q_tab[kMaxComponents];                          // indices into the batch's MultTable array
-    uint8_t pad0;
+    uint8_t raw_skew;      // raw, gathered row by row: row r of the staged payload starts
+                           // (src_addr + r * width * 3) & 15 bytes into its raw_pitch-wide slot
     // The crop box decides how much of the image is needed: the entropy decoder stops after
     // `mcu_rows` rows of MCUs and the inverse transform runs only on the MCUs of the box below
     // (the crop box grown by the reach of the chroma filter).  Whole image when there is no crop.
