@@ -161,7 +161,7 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
 // re-synchronise in two or three (long, fully parallel) rounds instead of dozens of chunks that
 // wait for one another.
 template <int kEntropyThreads, bool kStaged>
-__global__ void __launch_bounds__(kEntropyThreads)
+__global__ void __launch_bounds__(kEntropyThreads, 1536 / kEntropyThreads)
 entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
                         const uint8_t *__restrict__ blob, const HuffTable *__restrict__ huff,
                         uint8_t *__restrict__ clean, int16_t *__restrict__ coef,

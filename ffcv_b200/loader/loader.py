@@ -10,7 +10,7 @@ import torch as ch
 
 from .. import libffcv as L
 from ..fields.base import Field
-from ..memory_managers import MemoryManager, OSCacheManager
+from ..memory_managers import MemoryManager, OSCacheManager, ReadAheadManager
 from ..pipeline.compiler import Compiler
 from ..pipeline.graph import Graph
 from ..pipeline.operation import Operation
@@ -51,7 +51,10 @@ class Loader:
         count); < 1 means every core this process may run on.
     os_cache : bool
         The file is memory-mapped and served from the operating system's page cache.  ``False``
-        (the reference's process cache for datasets larger than RAM) maps the file too.
+        (the reference's process cache, for datasets larger than RAM) maps the file too, never
+        pins it, and lets the epoch's batch schedule drive the kernel's read-ahead: the byte
+        ranges of the next batches are requested ahead of time and those of finished batches are
+        handed back, so resident memory stays bounded.
     order : OrderOption or TraversalOrder subclass
         SEQUENTIAL, RANDOM, QUASI_RANDOM, or a custom order.
     distributed : bool
@@ -130,6 +133,8 @@ class Loader:
             pin_file = environ['FFCV_B200_PIN_FILE'] == '1'
         threads = num_workers if num_workers >= 1 else \
             len(sched_getaffinity(0)) // max(1, int(environ.get('LOCAL_WORLD_SIZE', '1')))
+        if not os_cache:
+            pin_file = False  # the file is taken to be larger than RAM
         if pin_file is None:
             limit = float(environ.get('FFCV_B200_PIN_LIMIT_GB', '64')) * (1 << 30)
             pin_file = ch.cuda.is_available() and getsize(fname) <= limit
@@ -142,7 +147,15 @@ class Loader:
             self.stage_split = -1 if threads >= 8 else 0  # -1: balanced by the native context
         else:
             self.stage_split = int(round(cpu_stage_share * 1000))
-        self.memory_manager: MemoryManager = OSCacheManager(self.reader, pin=self.pin_file)
+        if os_cache:
+            self.memory_manager: MemoryManager = OSCacheManager(self.reader, pin=self.pin_file)
+        else:
+            # schedule-driven read-ahead over the mapping (the reference's process cache role)
+            md = self.reader.metadata
+            cols = [md[name]['data_ptr'] for name in md.dtype.names if 'data_ptr' in (md[name].dtype.names or ())]
+            ptrs = np.stack(cols, axis=1) if cols else np.zeros((self.reader.num_samples, 0), dtype=np.uint64)
+            self.memory_manager = ReadAheadManager(self.reader, ptrs, window=2 * (batches_ahead + 2),
+                                                   keep=batches_ahead + 3)
 
         if order in ORDER_MAP:
             self.traversal_order: TraversalOrder = ORDER_MAP[order](self)

@@ -1,3 +1,4 @@
 from .os_cache import MemoryManager, OSCacheManager
+from .read_ahead import ReadAheadManager
 
-__all__ = ['MemoryManager', 'OSCacheManager']
+__all__ = ['MemoryManager', 'OSCacheManager', 'ReadAheadManager']

@@ -153,3 +153,37 @@ def test_invalid_arguments(beton):
         Loader(beton, batch_size=8, order='shuffled', pipelines={'image': None})
     with pytest.raises(ValueError):
         Loader(beton, batch_size=8, pipelines={'image': None, 'label': 5})
+
+
+def test_read_ahead_manager_follows_the_schedule(beton):
+    """os_cache=False: the byte ranges of upcoming batches are requested ahead of the pipeline and
+    released behind it (a recording stand-in replaces posix_fadvise); results are unchanged."""
+    import os
+    from ffcv_b200.memory_managers import ReadAheadManager
+    from ffcv_b200.memory_managers.read_ahead import merge_ranges
+    assert merge_ranges([10000, 100, 5000000], [50, 5000, 10]) == [(0, 12288), (4997120, 4096)]
+    truth = _labels(beton)
+    loader = _loader(beton, batch_size=32, drop_last=False, os_cache=False)
+    mm = loader.memory_manager
+    assert isinstance(mm, ReadAheadManager) and not loader.pin_file
+    calls = []
+    mm.advise = lambda fd, start, length, flag: calls.append((start, length, flag))
+    got = ch.cat([b[0].clone() for b in loader]).numpy().ravel()
+    assert np.array_equal(got, truth)
+    loader._live_iterator.retire() if loader._live_iterator is not None else None
+    want = [c for c in calls if c[2] == os.POSIX_FADV_WILLNEED]
+    drop = [c for c in calls if c[2] == os.POSIX_FADV_DONTNEED]
+    assert want and drop
+    # every sample's payload lies inside a requested range
+    ptrs = loader.reader.metadata['f0']['data_ptr']
+    sizes = mm.sizes_of(ptrs)
+    covered = np.zeros(len(ptrs), bool)
+    for start, length, _ in want:
+        covered |= (ptrs >= start) & (ptrs + sizes <= start + length)
+    assert covered.all()
+    # nothing is released before it was requested
+    first_want = {}
+    for k, c in enumerate(calls):
+        if c[2] == os.POSIX_FADV_WILLNEED:
+            first_want.setdefault(c[:2], k)
+    assert all(first_want.get(c[:2], -1) < k for k, c in enumerate(calls) if c[2] == os.POSIX_FADV_DONTNEED)
