@@ -78,7 +78,7 @@ def dataset_path(images, restart_interval=0):
 
 def ensure_dataset(images, restart_interval=0):
     """Written once (rank 0) before any timing; other ranks wait for the barrier that follows."""
-    from ffcv_b200.synthetic import replicate_samples, write_dataset
+    from ffcv_b200.synthetic import replicate_samples, write_dataset_isolated as write_dataset  # forks workers
     path = dataset_path(images, restart_interval)
     if not os.path.exists(path):
         tmp = path + f'.tmp{os.getpid()}'

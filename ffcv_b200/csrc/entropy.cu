@@ -195,9 +195,14 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
     }
     if (tid < 64) s_zz[tid] = kZigzagNatural[tid];
 
-    // ---- remove byte stuffing (FF 00 -> FF) into the clean stream
+    // ---- remove byte stuffing (FF 00 -> FF) into the clean stream.  When the whole scan fits the
+    // shared-memory stream buffer (the usual case: the subsequence length is chosen so that the
+    // largest image of the batch is one chunk) the clean stream is built there and never touches
+    // global memory; otherwise it goes to the scratch buffer and is staged chunk by chunk.
     const uint8_t *scan = blob + d.payload_off + d.scan_off;
-    uint8_t *cl = clean + d.clean_off;
+    const uint32_t stream_bytes = kStaged ? ((uint32_t)kEntropyThreads * (uint32_t)subseq_bits / 8 + 63) / 16 * 16 + 16 : 0;
+    const bool resident = kStaged && d.scan_len + 80 <= stream_bytes; // 64 zero bytes follow the stream
+    uint8_t *cl = resident ? reinterpret_cast<uint8_t *>(s_stream) : clean + d.clean_off;
     uint32_t clean_len = 0;
     for (uint32_t base = 0; base < d.scan_len; base += kEntropyThreads * 16) {
         const uint32_t my = base + tid * 16;
@@ -232,7 +237,10 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
     Cursor zero = {0, 0, 0};
     unsigned long long carry = pack(zero);
     uint32_t blk_base = 0;
-    for (;;) {
+    // every chunk moves the carry forward by at least one subsequence; the count is bounded all the
+    // same so that no input, however malformed, can keep the kernel running
+    const uint32_t max_chunks = total_bits / S + 2;
+    for (uint32_t chunk = 0; chunk < max_chunks; chunk++) {
         const uint32_t carry_p = (uint32_t)(carry >> 32);
         if (carry_p >= total_bits || blk_base >= d.nblocks) break;
         const uint32_t first_sub = carry_p / S;
@@ -258,9 +266,9 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         // The chunk's bits go to shared memory: every lane of a warp reads a different part of the
         // stream for every symbol, which shared memory serves at a few cycles per warp while the
         // same pattern on global memory saturates the L1 tag stage (one sector lookup per cycle).
-        const uint32_t bit_base = kStaged ? first_sub * S : 0; // S is a multiple of 128: 16-byte aligned in the stream
+        const uint32_t bit_base = (kStaged && !resident) ? first_sub * S : 0; // S is a multiple of 128: 16-byte aligned in the stream
         const uint32_t *stream = kStaged ? s_stream : words;
-        if (kStaged) {
+        if (kStaged && !resident) {
             uint32_t n16 = ((uint32_t)nsub * S + 127) / 128 + 1; // one vector of overrun for the last symbol
             const uint32_t have16 = (clean_len + 64 - (bit_base >> 3)) / 16; // zero padding included
             if (n16 > have16) n16 = have16;

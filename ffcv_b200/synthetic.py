@@ -6,6 +6,8 @@ fair coin, and per channel a smooth field ``128 + sum_m a_m sin(2 pi (cx_m x / W
 phi_m)`` of 8 low-frequency sinusoids (``a ~ U(8, 32)``, ``cx, cy ~ U(-4, 4)`` cycles,
 ``phi ~ U(0, 2 pi)``) plus Gaussian noise ``sigma = 8``, rounded and clipped to uint8.
 """
+import os
+
 import numpy as np
 
 
@@ -132,6 +134,20 @@ def write_dataset(cfg_id, path, count=None, num_workers=-1, page_size=None, rest
     writer = DatasetWriter(path, {'image': make_field(cfg_id, restart_interval), 'label': IntField()},
                            num_workers=num_workers, **kwargs)
     writer.from_indexed_dataset(SyntheticImageDataset(cfg_id, count), chunksize=16)
+    return path
+
+
+def write_dataset_isolated(cfg_id, path, count=None, num_workers=-1, page_size=None, restart_interval=0):
+    """`write_dataset` in a fresh interpreter.  The writer forks its workers (as the reference's
+    does); forking a process that already runs CUDA, NCCL or thread pools can deadlock the children,
+    so programs that have initialised any of those write their datasets through this call."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ('import sys; sys.path.insert(0, %r); from ffcv_b200.synthetic import write_dataset; '
+            'write_dataset(%r, %r, %r, %r, %r, %r)' % (root, cfg_id, path, count, num_workers, page_size, restart_interval))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES='')
+    subprocess.run([sys.executable, '-c', code], check=True, env=env)
     return path
 
 

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope='module')
 def datasets(tmp_path_factory):
-    from ffcv_b200.synthetic import write_dataset
+    from ffcv_b200.synthetic import write_dataset_isolated as write_dataset  # forks: not from this process
     d = tmp_path_factory.mktemp('betons')
     out = {}
     for cfg, n in [(0, 1536), (1, 192), (2, 128), (4, 6)]:
@@ -100,7 +100,7 @@ def test_streams_with_restart_markers(tmp_path, cfg, interval, res):
     thread (no speculation); the pixels must be those of the oracle, crop-limited decode included."""
     from ffcv_b200 import OrderOption
     from ffcv_b200.fields.decoders import RandomResizedCropRGBImageDecoder, SimpleRGBImageDecoder
-    from ffcv_b200.synthetic import write_dataset
+    from ffcv_b200.synthetic import write_dataset_isolated as write_dataset
     from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, ToTorchImage
     n = 6 if cfg == 4 else 64
     path = write_dataset(cfg, str(tmp_path / f'c{cfg}_rst{interval}.beton'), n, num_workers=4, restart_interval=interval)

@@ -96,7 +96,7 @@ def test_loader_pipeline_with_jitter_mixup_and_poison(tmp_path):
     from ffcv_b200 import Loader, OrderOption
     from ffcv_b200.fields.decoders import IntDecoder, RandomResizedCropRGBImageDecoder
     from ffcv_b200.pipeline.sampling import batch_seed, sample_jitter
-    from ffcv_b200.synthetic import write_dataset
+    from ffcv_b200.synthetic import write_dataset_isolated as write_dataset
     from ffcv_b200.transforms import (ImageMixup, LabelMixup, MixupToOneHot, NormalizeImage, Poison, RandomBrightness,
                                       RandomContrast, RandomHorizontalFlip, RandomSaturation, ToDevice, ToTensor,
                                       ToTorchImage)
