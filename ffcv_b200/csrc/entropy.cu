@@ -58,10 +58,10 @@ __device__ __forceinline__ uint32_t peek32(const uint32_t *__restrict__ words, u
     return __funnelshift_l(words[i + 1], words[i], p);
 }
 
-// Length and symbol of the Huffman code at the top of w: at most two dependent table reads.  An
-// invalid code consumes 16 bits and yields symbol 0, so that speculative decoding always makes
-// progress.
-__device__ __forceinline__ void huff_lookup(const HuffTable &t, uint32_t w, int &len, int &sym) {
+// Entry (see HuffTable) of the Huffman code at the top of w: at most two dependent table reads.
+// An invalid code consumes 16 bits and acts as an end of block, so that speculative decoding
+// always makes progress.
+__device__ __forceinline__ uint32_t huff_lookup(const HuffTable &t, uint32_t w) {
     uint32_t e = t.look[w >> 23];
     if (e & 0x8000u) {
         if (e != 0xFFFFu) {
@@ -74,14 +74,13 @@ __device__ __forceinline__ void huff_lookup(const HuffTable &t, uint32_t w, int 
             for (int l = 10; l <= 16; l++) {
                 const int c = code >> (16 - l);
                 if (c <= t.maxcode[l]) {
-                    e = (uint32_t)(l << 8) | t.vals[(t.valoff[l] + c) & 255];
+                    e = huff_entry(l, t.vals[(t.valoff[l] + c) & 255]);
                     break;
                 }
             }
         }
     }
-    len = e ? (int)(e >> 8) : 16;
-    sym = (int)(e & 255);
+    return e ? e : (16u | (63u << 9));
 }
 
 __device__ __forceinline__ int extend(uint32_t bits, int s) {
@@ -127,17 +126,15 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
         const uint32_t w = peek32(words, p - bit_base);
         const bool dc = z == 0;
         const HuffTable &t = s_tab[comp2 + (dc ? 0 : 1)];
-        int len, sym;
-        huff_lookup(t, w, len, sym);
-        const int s = sym & 15, r = sym >> 4;
-        const int zpos = dc ? 0 : z + r; // where this symbol's coefficient goes, if it has one
+        const uint32_t e = huff_lookup(t, w);
+        const int n = e & 31, s = (e >> 5) & 15;
+        const int zn = dc ? 1 : z + (int)(e >> 9); // DC: on to the first AC position
         if (WRITE) {
+            // where this symbol's coefficient goes, if it has one
+            const int zpos = zn - 1;
             if (s != 0 && zpos < 64 && blk < nblocks)
-                out[dc ? 0 : s_zz[zpos]] = (int16_t)extend((w << len) >> (32 - s), s);
+                out[dc ? 0 : s_zz[zpos]] = (int16_t)extend((w << (n - s)) >> (32 - s), s);
         }
-        // AC without magnitude bits: end of block, or (r == 15) a run of 16 zeros
-        const int zn = (dc | (s != 0)) ? zpos + 1 : (r == 15 ? z + 16 : 64);
-        const int n = len + s;
         p += n;
         const bool eob = zn >= 64;
         z = eob ? 0 : zn;
@@ -386,19 +383,18 @@ __device__ __forceinline__ uint32_t decode_interval(const uint32_t *__restrict__
         const bool dc = z == 0;
         const int comp = (ncomp == 1 || c < luma) ? 0 : c - luma + 1;
         const HuffTable &t = s_tab[2 * comp + (dc ? 0 : 1)];
-        int len, sym;
-        huff_lookup(t, w, len, sym);
-        const int s = sym & 15, r = sym >> 4;
-        const int zpos = dc ? 0 : z + r;
-        const int v = s ? extend((w << len) >> (32 - s), s) : 0;
+        const uint32_t e = huff_lookup(t, w);
+        const int n = e & 31, s = (e >> 5) & 15;
+        const int zn = dc ? 1 : z + (int)(e >> 9);
+        const int zpos = zn - 1;
+        const int v = s ? extend((w << (n - s)) >> (32 - s), s) : 0;
         if (dc) {
             pred[comp] += v;
             out[0] = (int16_t)pred[comp];
         } else if (s != 0 && zpos < 64) {
             out[s_zz[zpos]] = (int16_t)v;
         }
-        const int zn = (dc | (s != 0)) ? zpos + 1 : (r == 15 ? z + 16 : 64);
-        p += len + s;
+        p += n;
         if (zn >= 64) {
             z = 0;
             done++;

@@ -130,7 +130,7 @@ void build_huff_table(const RawHuff &raw, HuffTable *t) {
     for (int len = 1; len <= 16; len++) {
         for (int i = 0; i < raw.bits[len]; i++, k++, code++) {
             if (code >= (1 << len)) continue; // over-subscribed table: ignore the excess codes
-            const uint16_t entry = (uint16_t)((len << 8) | raw.vals[k]);
+            const uint16_t entry = huff_entry(len, raw.vals[k]);
             if (len <= 9) {
                 const int first = code << (9 - len);
                 for (int f = 0; f < (1 << (9 - len)); f++) t->look[first + f] = entry;

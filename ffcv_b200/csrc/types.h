@@ -48,16 +48,31 @@ struct ImageDesc {
 // Canonical Huffman code (ITU-T T.81 Annex C) prepared for table-driven decoding.
 constexpr int kHuffSubTables = 8; // the standard tables need 5; others fall back to the code-length walk
 struct HuffTable {
-    // First level, indexed by the next 9 bits: (code length << 8) | symbol for codes of up to 9
-    // bits; 0x8000 | k when the code is longer and continues in sub[k]; 0xFFFF when it is longer
+    // Table entries describe what a code does to the decoder rather than what it is (see
+    // huff_entry): bits 0-4 the bits the symbol consumes (code + magnitude bits), bits 5-8 the
+    // number of magnitude bits, bits 9-14 the zig-zag positions an AC symbol advances (run + 1;
+    // 16 for a run of zeros; 63 for an end of block, which always reaches the block's end).
+    // First level, indexed by the next 9 bits: such an entry for codes of up to 9 bits;
+    // 0x8000 | k when the code is longer and continues in sub[k]; 0xFFFF when it is longer
     // and no sub-table was left (walk maxcode/valoff instead); 0 for an invalid prefix.
     uint16_t look[512];
-    // Second level, indexed by bits 10..16 of the code: (code length << 8) | symbol, 0 if invalid.
+    // Second level, indexed by bits 10..16 of the code: an entry as above, 0 if invalid.
     uint16_t sub[kHuffSubTables][128];
     int32_t maxcode[18]; // largest code of each length, -1 if none
     int32_t valoff[17];  // index of the first symbol of each length minus its first code
     uint8_t vals[256];
 };
+
+// Entry of a code of `len` bits for symbol `sym` (run << 4 | magnitude bits).  A symbol without
+// magnitude bits is a run of 16 zeros when its run field is 15 and ends the block otherwise.
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline uint16_t huff_entry(int len, int sym) {
+    const int s = sym & 15, r = sym >> 4;
+    const int dz = s != 0 ? r + 1 : (r == 15 ? 16 : 63);
+    return (uint16_t)((len + s) | (s << 5) | (dz << 9));
+}
 
 // Dequantisation multipliers of the fast integer IDCT: quantiser step x AAN scale, 2 fraction bits.
 struct MultTable {
