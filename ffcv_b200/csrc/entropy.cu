@@ -69,7 +69,7 @@ __device__ __forceinline__ uint32_t huff_lookup(const HuffTable &t, uint32_t w) 
         } else {
             // more long-code prefixes than sub-tables (never with the tables encoders emit)
             const int code = w >> 16;
-            e = 0;
+            e = 16u | (63u << 9); // no code at all: a 16-bit end of block
 #pragma unroll 1
             for (int l = 10; l <= 16; l++) {
                 const int c = code >> (16 - l);
@@ -80,7 +80,7 @@ __device__ __forceinline__ uint32_t huff_lookup(const HuffTable &t, uint32_t w) 
             }
         }
     }
-    return e ? e : (16u | (63u << 9));
+    return e;
 }
 
 __device__ __forceinline__ int extend(uint32_t bits, int s) {
@@ -264,7 +264,8 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         // stream for every symbol, which shared memory serves at a few cycles per warp while the
         // same pattern on global memory saturates the L1 tag stage (one sector lookup per cycle).
         const uint32_t bit_base = (kStaged && !resident) ? first_sub * S : 0; // S is a multiple of 128: 16-byte aligned in the stream
-        const uint32_t *stream = kStaged ? s_stream : words;
+        // the staged copy starts at bit_base: a pointer moved back by that many words takes absolute bit positions
+        const uint32_t *stream = (kStaged ? s_stream : words) - (bit_base >> 5);
         if (kStaged && !resident) {
             uint32_t n16 = ((uint32_t)nsub * S + 127) / 128 + 1; // one vector of overrun for the last symbol
             const uint32_t have16 = (clean_len + 64 - (bit_base >> 3)) / 16; // zero padding included
@@ -301,7 +302,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
                 Cursor cur = unpack(in);
                 uint32_t t_end = (first_sub + (uint32_t)t + 1) * S;
                 if (t_end > total_bits) t_end = total_bits;
-                s_blocks[t] = (uint16_t)decode_span<false>(stream, bit_base, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
+                s_blocks[t] = (uint16_t)decode_span<false>(stream, 0, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
                 const unsigned long long out = pack(cur);
                 if (s_state[t + 1] != out) { // only this thread writes entry t + 1 in this round
                     s_state[t + 1] = out;
@@ -315,7 +316,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         const int first = block_scan_exclusive(my_blocks, s_warp, chunk_blocks);
         if (active) {
             Cursor cur = unpack(s_state[tid]);
-            decode_span<true>(stream, bit_base, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
+            decode_span<true>(stream, 0, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
                               blk_base + (uint32_t)first, d.nblocks);
         }
         carry = s_state[nsub];

@@ -155,6 +155,14 @@ void build_huff_table(const RawHuff &raw, HuffTable *t) {
         }
         code <<= 1;
     }
+    // A bit pattern that is no code acts as a 16-bit end of block (the decoder must make progress
+    // on garbage too): written into the tables, so the look-up needs no special case.
+    const uint16_t invalid = (uint16_t)(16 | (63 << 9));
+    for (int i = 0; i < 512; i++)
+        if (t->look[i] == 0) t->look[i] = invalid;
+    for (int k = 0; k < n_sub; k++)
+        for (int i = 0; i < 128; i++)
+            if (t->sub[k][i] == 0) t->sub[k][i] = invalid;
 }
 
 void build_mult_table(const uint16_t quant[64], MultTable *out) {

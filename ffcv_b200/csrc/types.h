@@ -54,9 +54,10 @@ struct HuffTable {
     // 16 for a run of zeros; 63 for an end of block, which always reaches the block's end).
     // First level, indexed by the next 9 bits: such an entry for codes of up to 9 bits;
     // 0x8000 | k when the code is longer and continues in sub[k]; 0xFFFF when it is longer
-    // and no sub-table was left (walk maxcode/valoff instead); 0 for an invalid prefix.
+    // and no sub-table was left (walk maxcode/valoff instead).  A prefix that is no code holds
+    // the entry of a 16-bit end of block.
     uint16_t look[512];
-    // Second level, indexed by bits 10..16 of the code: an entry as above, 0 if invalid.
+    // Second level, indexed by bits 10..16 of the code: an entry as above.
     uint16_t sub[kHuffSubTables][128];
     int32_t maxcode[18]; // largest code of each length, -1 if none
     int32_t valoff[17];  // index of the first symbol of each length minus its first code
