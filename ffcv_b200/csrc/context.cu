@@ -835,7 +835,6 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         const int32_t *jl = reinterpret_cast<const int32_t *>(blob + s.jpeg_list_off);
         const int32_t *pl = reinterpret_cast<const int32_t *>(blob + s.par_list_off);
         const int32_t *sl = reinterpret_cast<const int32_t *>(blob + s.seq_list_off);
-        if (s.total_blocks) CU(cudaMemsetAsync(s.coef.p, 0, (size_t)s.total_blocks * 128, st));
         launch_entropy_decode(descs, pl, s.n_par, sl, s.n_seq, blob, huff, (uint8_t *)s.clean.p,
                               (int16_t *)s.coef.p, status, s.subseq_bits, s.entropy_threads, st);
         if (prof) CU(cudaEventRecord(s.ev[2], st));

@@ -233,7 +233,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
 
     Cursor zero = {0, 0, 0};
     unsigned long long carry = pack(zero);
-    uint32_t blk_base = 0;
+    uint32_t blk_base = 0, zeroed_to = 0;
     // every chunk moves the carry forward by at least one subsequence; the count is bounded all the
     // same so that no input, however malformed, can keep the kernel running
     const uint32_t max_chunks = total_bits / S + 2;
@@ -314,6 +314,21 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         const int my_blocks = active ? s_blocks[tid] : 0;
         int chunk_blocks;
         const int first = block_scan_exclusive(my_blocks, s_warp, chunk_blocks);
+        // Only non-zero coefficients are stored, so the blocks this chunk writes to are cleared
+        // first: the ones it completes and the one left in progress at its end.  Done here rather
+        // than by a device-wide memset long before, the cleared lines are still in L2 when the
+        // coefficients arrive and reach DRAM once, as whole lines.
+        {
+            uint32_t target = blk_base + (uint32_t)chunk_blocks + 1;
+            if (target > d.nblocks) target = d.nblocks;
+            if (target > zeroed_to) {
+                uint4 *z16 = reinterpret_cast<uint4 *>(cf + (size_t)zeroed_to * 64);
+                const uint32_t nvec = (target - zeroed_to) * 8;
+                for (uint32_t k = tid; k < nvec; k += kEntropyThreads) z16[k] = make_uint4(0, 0, 0, 0);
+                zeroed_to = target;
+            }
+            __syncthreads();
+        }
         if (active) {
             Cursor cur = unpack(s_state[tid]);
             decode_span<true>(stream, 0, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
@@ -324,6 +339,11 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         __syncthreads();
     }
     if (tid == 0) status[img] = blk_base >= d.nblocks ? 0 : kErrData;
+    if (zeroed_to < d.nblocks) { // a stream that ended early: the blocks it never reached read as zero
+        uint4 *z16 = reinterpret_cast<uint4 *>(cf + (size_t)zeroed_to * 64);
+        const uint32_t nvec = (d.nblocks - zeroed_to) * 8;
+        for (uint32_t k = tid; k < nvec; k += kEntropyThreads) z16[k] = make_uint4(0, 0, 0, 0);
+    }
     __syncthreads();
 
     // ---- integrate the DC differences of each component over the scan
@@ -481,13 +501,19 @@ entropy_restart_kernel(const ImageDesc *__restrict__ descs, const int32_t *__res
     if (tid < 64) cl[(clean_len + tid) ^ 3u] = 0;
     __syncthreads();
 
-    // ---- one thread per restart interval
+    // ---- clear the image's blocks (only non-zero coefficients are stored), then one thread per
+    // restart interval
+    int16_t *cf = coef + (size_t)d.block_base * 64;
+    {
+        uint4 *z16 = reinterpret_cast<uint4 *>(cf);
+        for (uint32_t k = tid; k < d.nblocks * 8; k += kThreads) z16[k] = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
     const uint32_t *words = reinterpret_cast<const uint32_t *>(cl);
     const int bpm = d.bpm, luma = d.hs * d.vs, ncomp = d.ncomp;
     const int nmcu = d.mcus_x * d.mcu_rows; // the crop may need only the upper rows
     const uint32_t needed = (uint32_t)((nmcu + ri - 1) / ri);
     const uint32_t found = n_mark + 1 < cap ? n_mark + 1 : cap;
-    int16_t *cf = coef + (size_t)d.block_base * 64;
     if (found < needed) {
         if (tid == 0) s_bad = 1; // fewer intervals than the frame needs
     }

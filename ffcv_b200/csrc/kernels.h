@@ -21,7 +21,8 @@ constexpr int kMaxStagedBits = 1280;
 // of 32), `entropy_threads` (128, 256, 512 or 1024) the CTA size: one CTA decodes one image,
 // `entropy_threads` subsequences at a time.  Samples with restart markers are listed in `seq_list`
 // instead and take the restart-interval kernel (one thread per interval, no speculation; needs
-// descs[i].rst_off).  `coef` must be zeroed by the caller.
+// descs[i].rst_off).  `coef` needs no initialisation: the kernels clear
+// every block they decode into.
 void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
                            const int32_t *seq_list, int n_seq, const uint8_t *blob,
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,

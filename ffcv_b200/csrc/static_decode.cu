@@ -135,9 +135,6 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     // pageable source: the runtime has copied `m` out before this call returns
     if (cudaMemcpyAsync(meta_dev, &m, sizeof(m), cudaMemcpyHostToDevice, st) != cudaSuccess)
         return reject(FFCVB_E_CUDA, "copy of the descriptor failed");
-    // the array keeps the previous call's contents: coefficients must start at zero
-    if (cudaMemsetAsync(scratch + kCoefOff, 0, (size_t)d.nblocks * 128, st) != cudaSuccess)
-        return reject(FFCVB_E_CUDA, "clearing the coefficient scratch failed");
     const ImageDesc *desc_dev = &meta_dev->desc;
     const int32_t *list_dev = meta_dev->list; // {0}: the only image
     const bool sequential = d.restart_interval != 0;
