@@ -43,10 +43,10 @@ IMAGENET_STD = np.array([0.229, 0.224, 0.225]) * 255
 # summarised in profiles/config2_batch512_all_kernels.txt (same workload, 512-sample launches):
 # per JPEG sample for the three decode kernels, per sample for the fused resize kernel.
 NCU_DRAM_BYTES_PER_UNIT = {
-    'entropy_decode': (132.45e6 + 132.74e6) / 240,
-    'idct': (133.39e6 + 37.79e6) / 240,
-    'upsample_colour': (42.55e6 + 16.13e6) / 240,
-    'resize_augment_normalise': (137.33e6 + 109.50e6) / 512,
+    'entropy_decode': ((19.13e6 + 148.67e6) / 240 + (10.12e6 + 108.26e6) / 200) / 2,
+    'idct': ((69.30e6 + 11.66e6) / 240 + (59.13e6 + 5.72e6) / 200) / 2,
+    'upsample_colour': ((42.54e6 + 15.69e6) / 240 + (36.06e6 + 8.52e6) / 200) / 2,
+    'resize_augment_normalise': (128.75e6 + 108.14e6) / 512,
 }
 
 
