@@ -244,6 +244,8 @@ def main_ours(args):
     device = ch.device('cuda', local)
     if world > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        # stdout carries the one JSON line: whatever NCCL has to say (its version banner) goes to stderr
+        os.environ.setdefault('NCCL_DEBUG_FILE', '/dev/stderr')
         dist.init_process_group('nccl', device_id=device)
 
     def barrier():
