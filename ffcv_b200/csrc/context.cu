@@ -1077,6 +1077,24 @@ int ffcvb_poison(ffcvb_ctx *ctx, void *stream, uint8_t *images_dev, int n, int64
     return FFCVB_OK;
 }
 
+int ffcvb_host_register(void *ptr, uint64_t bytes) {
+    if (!ptr || bytes == 0) return FFCVB_E_ARG;
+    if (cudaHostRegister(ptr, (size_t)bytes, cudaHostRegisterDefault) != cudaSuccess) {
+        cudaGetLastError(); // refused (a read-only mapping, a file on disk): not an error of the process
+        return FFCVB_E_CUDA;
+    }
+    return FFCVB_OK;
+}
+
+int ffcvb_host_unregister(void *ptr) {
+    if (!ptr) return FFCVB_E_ARG;
+    if (cudaHostUnregister(ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return FFCVB_E_CUDA;
+    }
+    return FFCVB_OK;
+}
+
 // ------------------------------------------------------------ reference-signature entry points
 
 static ffcvb_ctx *g_ctx = nullptr;

@@ -61,6 +61,10 @@ lib.ffcvb_poison.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_voi
 lib.ffcvb_poison.restype = c_int
 lib.ffcvb_set_staging_split.argtypes = [c_void_p, c_int]
 lib.ffcvb_set_staging_split.restype = c_int
+lib.ffcvb_host_register.argtypes = [c_void_p, c_uint64]
+lib.ffcvb_host_register.restype = c_int
+lib.ffcvb_host_unregister.argtypes = [c_void_p]
+lib.ffcvb_host_unregister.restype = c_int
 lib.ffcvb_staging_split.argtypes = [c_void_p]
 lib.ffcvb_staging_split.restype = c_int
 lib.ffcvb_set_profiling.argtypes = [c_void_p, c_int]
@@ -123,6 +127,15 @@ def _as(a, dtype):
 
 class FFCVBError(RuntimeError):
     pass
+
+
+def host_register(address, nbytes):
+    """True when the range could be page-locked in place."""
+    return lib.ffcvb_host_register(address, nbytes) == 0
+
+
+def host_unregister(address):
+    return lib.ffcvb_host_unregister(address) == 0
 
 
 class Context:

@@ -77,8 +77,10 @@ class Loader:
     pin_file : bool
         (not in the reference) Keep the whole file in page-locked host memory and let the GPU
         fetch each batch's bytes itself over PCIe instead of staging them with CPU threads: the
-        bytes cross host memory once instead of three times, at the price of one pinned copy of
-        the file per process.  Default (``None``): on when the file is at most
+        bytes cross host memory once instead of three times.  A file on a memory file system
+        (``/dev/shm``) is page-locked where it lies, so all processes of a node share the one
+        copy and nothing is read at start-up; any other file costs one pinned copy per process.
+        Default (``None``): on when the file is at most
         ``FFCV_B200_PIN_LIMIT_GB`` (default 64) GiB.  Measured on config 2: 1 GPU + 16 threads
         255-270 k img/s staged, 250-270 k gathered, 300-330 k split (below); 8 GPUs + 32 cores
         326 k staged, 1.15 M gathered.  ``FFCV_B200_PIN_FILE`` = 0 / 1 overrides.

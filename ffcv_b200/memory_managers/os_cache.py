@@ -67,7 +67,9 @@ class OSCacheManager(MemoryManager):
         if self.mmap is None:
             if self.pin:
                 try:
-                    self.mmap = self._read_pinned()
+                    self.mmap = self._register_shared()
+                    if self.mmap is None:
+                        self.mmap = self._read_pinned()
                     self.pinned = True
                 except Exception as exc:  # not enough lockable memory, no CUDA: keep the staged path
                     print(f'ffcv_b200: could not pin {self.reader.file_name} ({exc}); using the page cache')
@@ -75,6 +77,50 @@ class OSCacheManager(MemoryManager):
             if self.mmap is None:
                 self.mmap = np.memmap(self.reader.file_name, 'uint8', mode='r')
         return self.mmap
+
+    def _register_shared(self):
+        """Page-locks the file's own pages in place: a shared, writable mapping of a file on a
+        memory file system (``/dev/shm``) can be registered with the CUDA driver, which makes the
+        page cache itself the pinned copy -- nothing is read at start-up and every process of the
+        node shares the one copy.  (Read-only mappings and files on disk are refused by the
+        driver; then the caller falls back to a private pinned copy.)  Nothing is ever written
+        through the mapping.  Returns None when the file cannot be registered."""
+        import mmap
+        import os
+        from .. import libffcv as L
+        try:
+            fd = os.open(self.reader.file_name, os.O_RDWR)
+        except OSError:
+            return None
+        try:
+            mm = mmap.mmap(fd, 0, flags=mmap.MAP_SHARED, prot=mmap.PROT_READ | mmap.PROT_WRITE)
+        except (OSError, ValueError):
+            os.close(fd)
+            return None
+        os.close(fd)
+        view = np.frombuffer(mm, dtype=np.uint8)
+        if not L.host_register(view.ctypes.data, view.size):
+            del view
+            mm.close()
+            return None
+        self._registered = (view.ctypes.data, mm)
+        view.flags.writeable = False
+        return view
+
+    def close(self):
+        """Releases the page lock taken by `_register_shared` (the mapping itself lives as long as
+        arrays that view it)."""
+        reg = getattr(self, '_registered', None)
+        if reg is not None:
+            from .. import libffcv as L
+            L.host_unregister(reg[0])
+            self._registered = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
     def _read_pinned(self):
         import os

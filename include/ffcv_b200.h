@@ -122,6 +122,15 @@ int ffcvb_set_async_staging(ffcvb_ctx *ctx, int enabled);
  * down.  Ignored for a pageable `file_base`.  No counterpart in the reference. */
 int ffcvb_set_staging_split(ffcvb_ctx *ctx, int cpu_share_permille);
 
+/* Page-locks `bytes` at `ptr` in place (cudaHostRegister) so that ffcvb_stage_batch treats a
+ * `file_base` inside that range as a pinned source.  Meant for a shared, writable mapping of a
+ * dataset file on a memory file system: the page cache itself becomes the pinned copy and every
+ * process of the node shares it.  Returns FFCVB_E_CUDA when the driver refuses (read-only
+ * mappings and files on disk are refused) and leaves no CUDA error behind.  No counterpart in
+ * the reference. */
+int ffcvb_host_register(void *ptr, uint64_t bytes);
+int ffcvb_host_unregister(void *ptr);
+
 /* The share (per mille) the next batch will be staged with. */
 int ffcvb_staging_split(const ffcvb_ctx *ctx);
 

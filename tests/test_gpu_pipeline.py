@@ -245,3 +245,34 @@ def test_corrupt_jpeg_is_reported_not_fatal(datasets, tmp_path):
     assert status[5] != 0 and status[3] != 0
     assert (np.delete(status, [3, 5]) == 0).all()
     assert batch[0].shape == (16, 64, 64, 3)
+
+
+def test_file_on_memory_file_system_is_pinned_in_place(tmp_path):
+    """A .beton on /dev/shm is page-locked where it lies (one copy for every process of the node);
+    on disk the loader falls back to a private pinned copy.  Same pixels either way."""
+    import shutil
+    import uuid
+    from ffcv_b200 import OrderOption
+    from ffcv_b200.fields.decoders import RandomResizedCropRGBImageDecoder
+    from ffcv_b200.synthetic import write_dataset_isolated
+    from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, ToTorchImage
+    if not (os.path.isdir('/dev/shm') and os.access('/dev/shm', os.W_OK)):
+        pytest.skip('no writable /dev/shm')
+    disk = write_dataset_isolated(2, str(tmp_path / 'c2.beton'), 48, num_workers=2)
+    shm = f'/dev/shm/ffcv_b200_test_{uuid.uuid4().hex}.beton'
+    shutil.copy(disk, shm)
+    try:
+        for path, in_place in [(shm, True), (disk, False)]:
+            pipes = {'image': [RandomResizedCropRGBImageDecoder((96, 96)), RandomHorizontalFlip(),
+                               NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()], 'label': None}
+            loader = _loader(path, 16, pipes, order=OrderOption.QUASI_RANDOM, pin_file=True)
+            mm = loader.memory_manager
+            mm.open()
+            assert mm.pinned
+            assert (getattr(mm, '_registered', None) is not None) == in_place or not in_place
+            compare_epoch(loader)
+            if loader._live_iterator is not None:
+                loader._live_iterator.retire()
+            del loader
+    finally:
+        os.remove(shm)
