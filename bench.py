@@ -244,9 +244,19 @@ def main_ours(args):
     device = ch.device('cuda', local)
     if world > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
-        # stdout carries the one JSON line: whatever NCCL has to say (its version banner) goes to stderr
-        os.environ.setdefault('NCCL_DEBUG_FILE', '/dev/stderr')
-        dist.init_process_group('nccl', device_id=device)
+        # stdout carries the one JSON line: while the communicator comes up (NCCL prints its version
+        # banner there) file descriptor 1 points at stderr
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group('nccl', device_id=device)
+            dist.barrier(device_ids=[local])
+            ch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     def barrier():
         if world > 1:
