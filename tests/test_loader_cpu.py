@@ -153,6 +153,8 @@ def test_invalid_arguments(beton):
         Loader(beton, batch_size=8, order='shuffled', pipelines={'image': None})
     with pytest.raises(ValueError):
         Loader(beton, batch_size=8, pipelines={'image': None, 'label': 5})
+    with pytest.raises(ValueError):
+        Loader(beton, batch_size=8, pipelines={'image': None}, cpu_stage_share=1.5)
 
 
 def test_read_ahead_manager_follows_the_schedule(beton):
