@@ -87,10 +87,11 @@ class Loader:
     cpu_stage_share : float
         (not in the reference) With a pinned file, the share of every batch's bytes that up to
         four staging threads copy and the copy engine moves while the GPU gathers the rest.
-        Default (``None``): balanced from batch to batch by the native context when this rank has
-        at least 8 staging threads, else 0 -- with many GPUs per host the CPU copies compete with
-        every GPU's gather for host memory bandwidth (8 GPUs on 32 cores: 1.15 M img/s gathered,
-        0.89 M balanced, 0.72 M at a fixed 0.3).
+        Default (``None``): balanced from batch to batch by the native context when this process
+        is the only rank on the host (``LOCAL_WORLD_SIZE`` <= 1) and has at least 8 staging
+        threads, else 0 -- with several GPUs per host the CPU copies compete with every GPU's
+        gather for host memory bandwidth (1 GPU + 16 cores: 305 k img/s balanced, 280 k gathered;
+        2 GPUs + 24 cores: 570 k vs 563 k; 8 GPUs + 32 cores: 0.89 M vs 1.15 M).
     """
 
     def __init__(self, fname: str, batch_size: int, num_workers: int = -1,
@@ -146,7 +147,10 @@ class Loader:
         if cpu_stage_share is not None and not 0 <= cpu_stage_share <= 1:
             raise ValueError("cpu_stage_share must lie in [0, 1]")
         if cpu_stage_share is None:
-            self.stage_split = -1 if threads >= 8 else 0  # -1: balanced by the native context
+            # -1: balanced by the native context.  Only for a GPU that has the host to itself: with
+            # two GPUs per host the split measured level with the pure gather, with eight it lost.
+            alone = int(environ.get('LOCAL_WORLD_SIZE', '1')) <= 1
+            self.stage_split = -1 if (threads >= 8 and alone) else 0
         else:
             self.stage_split = int(round(cpu_stage_share * 1000))
         if os_cache:
