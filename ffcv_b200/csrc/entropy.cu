@@ -201,17 +201,28 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
     const bool resident = kStaged && d.scan_len + 80 <= stream_bytes; // 64 zero bytes follow the stream
     uint8_t *cl = resident ? reinterpret_cast<uint8_t *>(s_stream) : clean + d.clean_off;
     uint32_t clean_len = 0;
-    for (uint32_t base = 0; base < d.scan_len; base += kEntropyThreads * 16) {
-        const uint32_t my = base + tid * 16;
+    // Every thread takes one aligned 16-byte word of the scan per pass (one load instead of sixteen);
+    // the byte before it, which decides whether a leading 00 is stuffing, comes from the lane below.
+    const uint32_t lead = (uint32_t)(reinterpret_cast<uintptr_t>(scan) & 15); // bytes of the first word before the scan
+    const uint4 *scan16 = reinterpret_cast<const uint4 *>(scan - lead);
+    for (uint32_t base = 0; base < d.scan_len + lead; base += kEntropyThreads * 16) {
+        const uint32_t chunk = base + tid * 16;         // offset of this thread's word from scan - lead
+        const int my = (int)chunk - (int)lead;           // scan offset of its first byte (negative in the first word)
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (chunk < d.scan_len + lead) v = scan16[chunk >> 4];
+        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
         uint8_t b[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) b[i] = (uint8_t)(wv[i >> 2] >> (8 * (i & 3)));
+        int prev = __shfl_up_sync(0xffffffffu, (int)b[15], 1);
+        if ((tid & 31) == 0) prev = (my > 0 && my <= (int)d.scan_len) ? scan[my - 1] : 0;
         uint32_t keep = 0;
-        int prev = (my > 0 && my <= d.scan_len) ? scan[my - 1] : 0;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            const uint32_t at = my + i;
-            b[i] = at < d.scan_len ? scan[at] : 0;
-            if (at < d.scan_len && !(b[i] == 0 && prev == 0xFF)) keep |= 1u << i;
-            prev = b[i];
+            const int at = my + i;
+            const bool inside = at >= 0 && at < (int)d.scan_len;
+            if (inside && !(b[i] == 0 && prev == 0xFF)) keep |= 1u << i;
+            prev = inside ? b[i] : 0;
         }
         int total;
         int off = block_scan_exclusive(__popc(keep), s_warp, total);
