@@ -96,8 +96,12 @@ const char *ffcvb_last_error(const ffcvb_ctx *ctx);
  * file_base[ptrs[i] .. ptrs[i] + sizes[i]), the byte range `memory_read` returns in
  * ffcv/memory_managers/os_cache.py:55-60) into the slot's pinned buffer with the staging threads,
  * parses JPEG headers, and lays out the device work.  modes/heights/widths are the per-sample
- * metadata columns of ffcv/fields/rgb_image.py:301-308.  Raw samples stage only the rows their
- * crop box touches.  Host-only; does not touch the GPU except to grow buffers. */
+ * metadata columns of ffcv/fields/rgb_image.py:301-308.  Raw samples stage only their crop box.
+ * When `file_base` lies in page-locked, device-mapped host memory (cudaHostAlloc, or
+ * ffcvb_host_register below) nothing is copied here: ffcvb_submit_batch lets the GPU fetch the
+ * payloads itself over PCIe (see ffcvb_set_staging_split for sharing that work with the staging
+ * threads); 16-byte words around a payload may be read, never beyond the page that holds a byte
+ * of it.  Host-only; does not touch the GPU except to grow buffers. */
 int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const uint64_t *ptrs,
                       const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
                       const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params);
