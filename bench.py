@@ -42,6 +42,15 @@ IMAGENET_STD = np.array([0.229, 0.224, 0.225]) * 255
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per unit of work, from the ncu capture
 # summarised in profiles/config2_batch512_all_kernels.txt (same workload, 512-sample launches):
 # per JPEG sample for the three decode kernels, per sample for the fused resize kernel.
+# Warp instructions executed (smsp__inst_executed.sum) per unit of work, same captures: the decode
+# and resize kernels are bound by instruction issue, not by HBM.
+NCU_WARP_INST_PER_UNIT = {
+    'entropy_decode': (133.35e6 / 240 + 111.50e6 / 200) / 2,
+    'idct': (33.66e6 / 240 + 28.67e6 / 200) / 2,
+    'upsample_colour': (87.30e6 / 240 + 74.58e6 / 200) / 2,
+    'resize_augment_normalise': 321.94e6 / 512,
+}
+SM_COUNT, ISSUE_PER_SM_CLK = 148, 4  # B200: 148 SMs, four warp schedulers each, one instruction per clock
 NCU_DRAM_BYTES_PER_UNIT = {
     'entropy_decode': ((19.13e6 + 148.67e6) / 240 + (10.12e6 + 108.26e6) / 200) / 2,
     'idct': ((69.30e6 + 11.66e6) / 240 + (59.13e6 + 5.72e6) / 200) / 2,
@@ -431,10 +440,21 @@ def main_ours(args):
              'resize_augment_normalise': float(BATCH)}
     for n in names:
         kernels[n]['ncu_dram_bytes'] = NCU_DRAM_BYTES_PER_UNIT[n] * units[n]
+    # second roofline of every kernel: the time its instructions would need if every warp scheduler
+    # of the GPU issued one of them per clock (clock: the median SM clock sampled during the run)
+    sm_hz = (clocks['sm_mhz'] if clocks and clocks.get('sm_mhz') else 1965.0) * 1e6
+    for n in names:
+        inst = NCU_WARP_INST_PER_UNIT[n] * units[n]
+        floor_ms = inst / (SM_COUNT * ISSUE_PER_SM_CLK * sm_hz) * 1e3
+        kernels[n]['issue'] = {'warp_instructions': inst, 'floor_ms': floor_ms, 'frac': floor_ms / kernels[n]['ms']}
     roofline = {'bound': 'hbm', 'kernel': dom, 'achieved': kernels[dom]['gbs'], 'peak': peak, 'unit': 'GB/s',
                 'frac': kernels[dom]['gbs'] / peak, 'traffic': kernels[dom]['ncu_dram_bytes'], 'peak_kind': peak_kind,
                 'traffic_source': 'ncu capture of the same workload, scaled by the JPEG samples per launch',
                 'ms_per_launch': kernels[dom]['ms'], 'kernels': kernels,
+                'issue': {'bound': 'integer issue (the binding one for this kernel)', 'unit': 'warp instructions/s',
+                          'achieved': kernels[dom]['issue']['warp_instructions'] / (kernels[dom]['ms'] * 1e-3),
+                          'peak': SM_COUNT * ISSUE_PER_SM_CLK * sm_hz, 'frac': kernels[dom]['issue']['frac'],
+                          'source': 'smsp__inst_executed.sum of the ncu capture, scaled by the JPEG samples per launch'},
                 'path': {'algorithmic_bytes_per_step': path_bytes, 'kernel_ms_per_step': total_kernel_ms,
                          'gbs': path_bytes / (total_kernel_ms * 1e-3) / 1e9}}
 
