@@ -171,7 +171,7 @@ struct DevBuf {
 struct Slot {
     uint8_t *host = nullptr; // pinned
     size_t host_cap = 0;
-    DevBuf blob, clean, coef, planes, rgb, status;
+    DevBuf blob, clean, coef, planes, rgb, status, ckpt;
     BatchHeader hdr{};
     ffcvb_plan plan{};
     int n = 0, n_jpeg = 0, n_par = 0, n_seq = 0, max_pixels = 0, subseq_bits = 512, entropy_threads = 512;
@@ -355,7 +355,7 @@ void ffcvb_destroy(ffcvb_ctx *ctx) {
     cudaDeviceSynchronize();
     for (auto &s : ctx->slots) {
         if (s.host) cudaFreeHost(s.host);
-        for (DevBuf *b : {&s.blob, &s.clean, &s.coef, &s.planes, &s.rgb, &s.status})
+        for (DevBuf *b : {&s.blob, &s.clean, &s.coef, &s.planes, &s.rgb, &s.status, &s.ckpt})
             if (b->p) cudaFree(b->p);
         for (auto &e : s.ev)
             if (e) cudaEventDestroy(e);
@@ -750,6 +750,10 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     if (const char *e = getenv("FFCV_B200_SUBSEQ_BITS")) s.subseq_bits = (atoi(e) + 127) / 128 * 128;
     if (const char *e = getenv("FFCV_B200_ENTROPY_THREADS")) s.entropy_threads = atoi(e);
     if (s.subseq_bits < 128) s.subseq_bits = 128;
+    {
+        const size_t need = entropy_checkpoint_bytes((int)par_list.size(), s.entropy_threads, s.subseq_bits);
+        if (need && (rc = grow_dev(ctx, s.ckpt, need))) return rc;
+    }
     s.scan_bytes = s.raw_bytes = s.jpeg_bytes = 0;
     for (int i = 0; i < n; i++) {
         if (descs[i].mode == FFCVB_MODE_JPG) {
@@ -836,7 +840,8 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         const int32_t *pl = reinterpret_cast<const int32_t *>(blob + s.par_list_off);
         const int32_t *sl = reinterpret_cast<const int32_t *>(blob + s.seq_list_off);
         launch_entropy_decode(descs, pl, s.n_par, sl, s.n_seq, blob, huff, (uint8_t *)s.clean.p,
-                              (int16_t *)s.coef.p, status, s.subseq_bits, s.entropy_threads, st);
+                              (int16_t *)s.coef.p, status, s.subseq_bits, s.entropy_threads,
+                              s.subseq_bits > kMaxStagedBits ? s.ckpt.p : nullptr, st);
         if (prof) CU(cudaEventRecord(s.ev[2], st));
         launch_idct(descs, jl, s.n_jpeg, s.total_blocks, mult, (const int16_t *)s.coef.p,
                     (uint8_t *)s.planes.p, st);

@@ -152,6 +152,69 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
     return done;
 }
 
+// Counting walk for long subsequences (the variant that reads the stream from global memory).
+// A re-decode of a long subsequence from a corrected entry state soon runs exactly where the
+// previous decode ran: the two walks merge once position, slot and zig-zag index coincide.  Every
+// walk therefore leaves its state at check-points every `ck_bits` bits; a later walk that finds
+// the same state at a check-point stops there -- the exit state stands and the block count is its
+// own count so far plus what the previous walk counted from that check-point to the end.  The repair pass
+// of a multi-megabit image then costs the re-synchronisation distance, not the whole subsequence.
+struct CheckPoint {
+    unsigned long long state; // pack(position, slot, zig-zag index)
+    uint32_t rest;            // blocks the walk completed from here to the end of the subsequence
+    uint32_t pad;
+};
+
+template <bool COMPARE>
+__device__ __forceinline__ int count_span_checked(const uint32_t *__restrict__ words, Cursor &cur, uint32_t start,
+                                                  uint32_t end, int bpm, int luma, int ncomp,
+                                                  const HuffTable *s_tab, CheckPoint *__restrict__ ck, uint32_t ck_bits,
+                                                  bool &merged) {
+    int done = 0;
+    uint32_t p = cur.p;
+    int c = cur.c, z = cur.z;
+    int comp2 = (ncomp == 1 || c < luma) ? 0 : 2 * (c - luma + 1);
+    const uint32_t k0 = (p - start) / ck_bits;
+    uint32_t k = k0;
+    uint32_t next_ck = start + (k + 1) * ck_bits;
+    int total = -1;
+    merged = false;
+    while (p < end) {
+        const uint32_t w = peek32(words, p);
+        const bool dc = z == 0;
+        const HuffTable &t = s_tab[comp2 + (dc ? 0 : 1)];
+        const uint32_t e = huff_lookup(t, w);
+        const int zn = dc ? 1 : z + (int)(e >> 9);
+        p += e & 31;
+        const bool eob = zn >= 64;
+        z = eob ? 0 : zn;
+        done += eob ? 1 : 0;
+        c = eob ? ((c + 1 == bpm) ? 0 : c + 1) : c;
+        comp2 = (ncomp == 1 || c < luma) ? 0 : 2 * (c - luma + 1);
+        if (p >= next_ck && p < end) {
+            Cursor here = {p, c, z};
+            const unsigned long long st = pack(here);
+            if (COMPARE && ck[k].state == st) {
+                merged = true; // from here on this walk is the previous one
+                total = done + (int)ck[k].rest;
+                break;
+            }
+            ck[k].state = st;
+            ck[k].rest = (uint32_t)done; // blocks so far; turned into blocks-to-the-end below
+            k++;
+            next_ck += ck_bits;
+        }
+    }
+    if (!merged) {
+        total = done;
+        cur.p = p;
+        cur.c = c;
+        cur.z = z;
+    }
+    for (uint32_t j = k0; j < k; j++) ck[j].rest = (uint32_t)total - ck[j].rest;
+    return total;
+}
+
 // kStaged: the chunk's bits are copied to shared memory first (subsequences of up to 1280 bits);
 // otherwise the threads read the unstuffed stream in global memory, which allows subsequences of
 // any length: a multi-megabit image is then one chunk of kEntropyThreads long subsequences that
@@ -162,7 +225,7 @@ __global__ void __launch_bounds__(kEntropyThreads, 1536 / kEntropyThreads)
 entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
                         const uint8_t *__restrict__ blob, const HuffTable *__restrict__ huff,
                         uint8_t *__restrict__ clean, int16_t *__restrict__ coef,
-                        int32_t *__restrict__ status, int subseq_bits) {
+                        int32_t *__restrict__ status, int subseq_bits, CheckPoint *__restrict__ ckpt, int ck_bits) {
     extern __shared__ __align__(16) uint32_t s_stream[]; // this chunk of the unstuffed stream
     __shared__ HuffTable s_tab[6];
     __shared__ unsigned long long s_state[kEntropyThreads + 1];
@@ -311,13 +374,31 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
             __syncthreads(); // every entry state is read before any exit state is written
             if (t >= 0) {
                 Cursor cur = unpack(in);
-                uint32_t t_end = (first_sub + (uint32_t)t + 1) * S;
+                const uint32_t t_start = (first_sub + (uint32_t)t) * S;
+                uint32_t t_end = t_start + S;
                 if (t_end > total_bits) t_end = total_bits;
-                s_blocks[t] = (uint16_t)decode_span<false>(stream, 0, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
-                const unsigned long long out = pack(cur);
-                if (s_state[t + 1] != out) { // only this thread writes entry t + 1 in this round
-                    s_state[t + 1] = out;
-                    s_dirty[t + 1] = 1;
+                bool merged = false;
+                if (!kStaged && ckpt != nullptr) {
+                    // long subsequences: stop where this walk rejoins the previous one
+                    const uint32_t per_sub = S / (uint32_t)ck_bits + 1;
+                    CheckPoint *ck = ckpt + ((size_t)blockIdx.x * kEntropyThreads + (size_t)t) * per_sub;
+                    int total;
+                    if (iter == 0)
+                        total = count_span_checked<false>(stream, cur, t_start, t_end, bpm, luma, ncomp, s_tab, ck,
+                                                          (uint32_t)ck_bits, merged);
+                    else
+                        total = count_span_checked<true>(stream, cur, t_start, t_end, bpm, luma, ncomp, s_tab, ck,
+                                                         (uint32_t)ck_bits, merged);
+                    s_blocks[t] = (uint16_t)total;
+                } else {
+                    s_blocks[t] = (uint16_t)decode_span<false>(stream, 0, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
+                }
+                if (!merged) {
+                    const unsigned long long out = pack(cur);
+                    if (s_state[t + 1] != out) { // only this thread writes entry t + 1 in this round
+                        s_state[t + 1] = out;
+                        s_dirty[t + 1] = 1;
+                    }
                 }
             }
             __syncthreads();
@@ -544,13 +625,14 @@ entropy_restart_kernel(const ImageDesc *__restrict__ descs, const int32_t *__res
 void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
                            const int32_t *seq_list, int n_seq, const uint8_t *blob,
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
-                           int subseq_bits, int entropy_threads, cudaStream_t stream) {
+                           int subseq_bits, int entropy_threads, void *checkpoints, cudaStream_t stream) {
     if (n_list > 0) {
         const bool staged = subseq_bits <= kMaxStagedBits;
         auto launch = [&](auto kernel, int threads) {
             const size_t smem = staged ? ((size_t)threads * subseq_bits / 8 + 63) / 16 * 16 + 16 : 16;
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<n_list, threads, smem, stream>>>(descs, list, blob, huff, clean, coef, status, subseq_bits);
+            kernel<<<n_list, threads, smem, stream>>>(descs, list, blob, huff, clean, coef, status, subseq_bits,
+                                                      static_cast<CheckPoint *>(checkpoints), kCheckPointBits);
         };
         switch (entropy_threads) {
         case 128:

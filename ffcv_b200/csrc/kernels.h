@@ -13,6 +13,13 @@ void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, cudaSt
 
 // Longest subsequence whose chunk the entropy decoder stages in shared memory.
 constexpr int kMaxStagedBits = 1280;
+// Longer subsequences leave check-points every kCheckPointBits bits (16 bytes each) so that a
+// repair pass can stop where it rejoins the previous pass: entropy_checkpoint_bytes() of scratch.
+constexpr int kCheckPointBits = 4096;
+inline size_t entropy_checkpoint_bytes(int n_images, int entropy_threads, int subseq_bits) {
+    if (subseq_bits <= kMaxStagedBits) return 0;
+    return (size_t)n_images * entropy_threads * (subseq_bits / kCheckPointBits + 1) * 16;
+}
 
 // Entropy decode of every JPEG sample listed in `list` (indices into descs): unstuffs the scan
 // into `clean`, Huffman-decodes it into quantised coefficients (natural order inside a block,
@@ -22,11 +29,13 @@ constexpr int kMaxStagedBits = 1280;
 // `entropy_threads` subsequences at a time.  Samples with restart markers are listed in `seq_list`
 // instead and take the restart-interval kernel (one thread per interval, no speculation; needs
 // descs[i].rst_off).  `coef` needs no initialisation: the kernels clear
-// every block they decode into.
+// every block they decode into.  `checkpoints`: entropy_checkpoint_bytes(n_list, ...) bytes of device
+// scratch when the subsequences are longer than kMaxStagedBits (may be nullptr: then every repair
+// pass walks its whole subsequence).
 void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
                            const int32_t *seq_list, int n_seq, const uint8_t *blob,
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
-                           int subseq_bits, int entropy_threads, cudaStream_t stream);
+                           int subseq_bits, int entropy_threads, void *checkpoints, cudaStream_t stream);
 
 // Dequantise + fast integer IDCT of `total_blocks` blocks into the 8-bit component planes.
 void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32_t total_blocks,
