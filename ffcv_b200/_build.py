@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 LIB = os.path.join(HERE, 'libffcv_b200.so')
-SOURCES = ['context.cu', 'entropy.cu', 'idct.cu', 'resize.cu', 'pixel_ops.cu', 'static_decode.cu', 'jpeg_header.cpp']
+SOURCES = ['context.cu', 'entropy.cu', 'idct.cu', 'gather.cu', 'resize.cu', 'pixel_ops.cu', 'static_decode.cu', 'jpeg_header.cpp']
 HEADERS = ['types.h', 'kernels.h', 'jpeg_header.h', os.path.join('..', '..', 'include', 'ffcv_b200.h')]
 
 

@@ -228,6 +228,9 @@ struct ffcvb_ctx {
     bool adaptive_split = false; // ... adjusted from batch to batch so that both sides take equally long
     double share = 0.0;          // the adjusted share, 0..1
     int split_copy_threads = 4; // ... and how many of them copy at a time (more only crowd the gather out)
+    // Tuning overrides, read from the environment once when the context is created (0 = none):
+    // FFCV_B200_COPY_THREADS, FFCV_B200_SUBSEQ_BITS, FFCV_B200_ENTROPY_THREADS, FFCV_B200_GATHER_CTAS.
+    int tune_copy_threads = 0, tune_subseq_bits = 0, tune_entropy_threads = 0, gather_ctas = 0;
     DevBuf one_src, one_dst; // single-image entry points
 };
 
@@ -344,6 +347,18 @@ int ffcvb_create(int device, int n_slots, int n_threads, ffcvb_ctx **out) {
     c->slots.resize(n_slots);
     for (int i = 0; i < n_slots; i++) c->wait_args.push_back(WaitArg{c, i});
     c->pool = new Pool(n_threads - 1);
+    auto env_int = [](const char *name, int lo, int hi) {
+        const char *e = getenv(name);
+        const int v = e ? atoi(e) : 0;
+        return v >= lo && v <= hi ? v : 0;
+    };
+    c->tune_copy_threads = env_int("FFCV_B200_COPY_THREADS", 1, 256);
+    c->tune_subseq_bits = (env_int("FFCV_B200_SUBSEQ_BITS", 128, 256 * 1024) + 127) / 128 * 128;
+    c->tune_entropy_threads = env_int("FFCV_B200_ENTROPY_THREADS", 128, 1024);
+    if (c->tune_entropy_threads != 128 && c->tune_entropy_threads != 256 && c->tune_entropy_threads != 512 &&
+        c->tune_entropy_threads != 1024)
+        c->tune_entropy_threads = 0; // only the CTA sizes the kernel is built for
+    c->gather_ctas = env_int("FFCV_B200_GATHER_CTAS", 1, 1024);
     *out = c;
     return FFCVB_OK;
 }
@@ -693,7 +708,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         Slot *sp = &s; // the job may outlive this call: it only touches slot-owned data and the source
         ctx->pool->wait(Pool::kAsync); // one copy at a time: the batch staged before this one
         int copy_threads = direct ? ctx->split_copy_threads : 0;
-        if (const char *e = getenv("FFCV_B200_COPY_THREADS")) copy_threads = atoi(e); // tuning override
+        if (ctx->tune_copy_threads) copy_threads = ctx->tune_copy_threads;
         {
             std::lock_guard<std::mutex> g(ctx->copy_m);
             s.copy_done = false;
@@ -746,10 +761,8 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.plane_bytes = plane_bytes;
     s.rgb_bytes = rgb_bytes;
     pick_entropy_config(scan_bytes_par, &s.entropy_threads, &s.subseq_bits);
-    // tuning overrides
-    if (const char *e = getenv("FFCV_B200_SUBSEQ_BITS")) s.subseq_bits = (atoi(e) + 127) / 128 * 128;
-    if (const char *e = getenv("FFCV_B200_ENTROPY_THREADS")) s.entropy_threads = atoi(e);
-    if (s.subseq_bits < 128) s.subseq_bits = 128;
+    if (ctx->tune_subseq_bits) s.subseq_bits = ctx->tune_subseq_bits;
+    if (ctx->tune_entropy_threads) s.entropy_threads = ctx->tune_entropy_threads;
     {
         const size_t need = entropy_checkpoint_bytes((int)par_list.size(), s.entropy_threads, s.subseq_bits);
         if (need && (rc = grow_dev(ctx, s.ckpt, need))) return rc;
@@ -819,7 +832,7 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         CU(cudaMemcpyAsync(blob, s.host, hd.payload_off, cudaMemcpyHostToDevice, s.gather_stream));
         CU(cudaEventRecord(s.ev_gather_start, s.gather_stream)); // after the head's copy: that one queues behind other batches' transfers
         s.gather_timed = true;
-        launch_gather_payloads(reinterpret_cast<const ImageDesc *>(blob + hd.desc_off), s.n, blob, s.gather_stream);
+        launch_gather_payloads(reinterpret_cast<const ImageDesc *>(blob + hd.desc_off), s.n, blob, ctx->gather_ctas, s.gather_stream);
         CU(cudaEventRecord(s.ev_gathered, s.gather_stream));
         if (s.staged_end > hd.payload_off) { // the CPU-staged share rides the copy engine meanwhile
             if ((hrc = hold_for_copy(ctx, s, st))) return hrc;
@@ -1175,5 +1188,13 @@ void resize(int64_t cresizer, int64_t source_p, int64_t sx, int64_t sy, int64_t 
 }
 
 void my_memcpy(void *source, void *dst, uint64_t size) { memcpy(dst, source, size); }
+
+void my_fread(int64_t fp, int64_t offset, void *destination, int64_t size) {
+    FILE *f = reinterpret_cast<FILE *>(static_cast<intptr_t>(fp));
+    if (!f || !destination || size <= 0 || offset < 0) return;
+    if (fseek(f, (long)offset, SEEK_SET) != 0) return;
+    size_t got = fread(destination, 1, (size_t)size, f);
+    (void)got;
+}
 
 } // extern "C"

@@ -9,7 +9,9 @@ namespace ffcvb {
 
 // Pulls every sample's payload from pinned host memory (descs[i].src_addr, read by the SMs over
 // PCIe) into its place in the device blob.  Source and destination share their alignment mod 16.
-void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, cudaStream_t stream);
+// `ctas`: CTAs of 256 threads that fetch (< 1: kGatherCtas).
+constexpr int kGatherCtas = 16;
+void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, int ctas, cudaStream_t stream);
 
 // Longest subsequence whose chunk the entropy decoder stages in shared memory.
 constexpr int kMaxStagedBits = 1280;

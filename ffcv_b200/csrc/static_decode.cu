@@ -89,6 +89,7 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     if (rc != 0) return reject(FFCVB_E_DECODE, "not a baseline JPEG stream this library decodes");
     if ((uint32_t)h.width != width || (uint32_t)h.height != height)
         return reject(FFCVB_E_DECODE, "stream dimensions differ from the given height and width");
+    if (height > 65535 || width > 65535) return reject(FFCVB_E_LIMIT, "image larger than FFCVB_STATIC_MAX_PADDED_PIXELS");
     Meta m;
     memset(&m, 0, sizeof(m));
     ImageDesc &d = m.desc;
@@ -115,7 +116,7 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
             return reject(FFCVB_E_LIMIT, "stream with restart markers too large for the static scratch");
     }
     const size_t luma_samples = (size_t)d.mcus_x * d.hs * 8 * d.mcus_y * d.vs * 8;
-    if (height > 65535 || width > 65535 || luma_samples > kMaxPaddedSamples)
+    if (luma_samples > kMaxPaddedSamples)
         return reject(FFCVB_E_LIMIT, "image larger than FFCVB_STATIC_MAX_PADDED_PIXELS");
     size_t plane = 0;
     for (int c = 0; c < h.ncomp; c++) {
@@ -132,7 +133,8 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     // ---- queue the work; everything the kernels need beyond input and output lives in `scratch`
     cudaStream_t st = (cudaStream_t)stream;
     Meta *meta_dev = reinterpret_cast<Meta *>(scratch);
-    // pageable source: the runtime has copied `m` out before this call returns
+    // `m` lives on this thread's stack (pageable memory): for such a source the runtime stages the
+    // bytes before cudaMemcpyAsync returns, so `m` may go out of scope when this call does
     if (cudaMemcpyAsync(meta_dev, &m, sizeof(m), cudaMemcpyHostToDevice, st) != cudaSuccess)
         return reject(FFCVB_E_CUDA, "copy of the descriptor failed");
     const ImageDesc *desc_dev = &meta_dev->desc;

@@ -80,8 +80,10 @@ class Loader:
         bytes cross host memory once instead of three times.  A file on a memory file system
         (``/dev/shm``) is page-locked where it lies, so all processes of a node share the one
         copy and nothing is read at start-up; any other file costs one pinned copy per process.
-        Default (``None``): on when the file is at most
-        ``FFCV_B200_PIN_LIMIT_GB`` (default 64) GiB.  Measured on config 2: 1 GPU + 16 threads
+        Default (``None``): a file of at most ``FFCV_B200_PIN_LIMIT_GB`` (default 64) GiB is
+        page-locked in place when it lies on a memory file system, and otherwise copied only if
+        the copies of all ranks of the host (``LOCAL_WORLD_SIZE``) fit half of the memory
+        available now; else the staged path is used.  Measured on config 2: 1 GPU + 16 threads
         255-270 k img/s staged, 250-270 k gathered, 300-330 k split (below); 8 GPUs + 32 cores
         326 k staged, 1.15 M gathered.  ``FFCV_B200_PIN_FILE`` = 0 / 1 overrides.
     cpu_stage_share : float
@@ -117,6 +119,9 @@ class Loader:
         }
         self.fname = fname
         self.batch_size = batch_size
+        if batches_ahead < 1:
+            # the slot ring's reuse argument needs a bounded queue: Queue(0) would be unbounded
+            raise ValueError("batches_ahead must be at least 1")
         self.batches_ahead = batches_ahead
         self.seed = seed
         self.reader = Reader(fname, custom_fields)
@@ -140,7 +145,7 @@ class Loader:
             pin_file = False  # the file is taken to be larger than RAM
         if pin_file is None:
             limit = float(environ.get('FFCV_B200_PIN_LIMIT_GB', '64')) * (1 << 30)
-            pin_file = ch.cuda.is_available() and getsize(fname) <= limit
+            pin_file = 'auto' if ch.cuda.is_available() and getsize(fname) <= limit else False
         self.pin_file = bool(pin_file)
         if cpu_stage_share is None and 'FFCV_B200_STAGE_SPLIT' in environ:
             cpu_stage_share = int(environ['FFCV_B200_STAGE_SPLIT']) / 1000
@@ -154,7 +159,10 @@ class Loader:
         else:
             self.stage_split = int(round(cpu_stage_share * 1000))
         if os_cache:
-            self.memory_manager: MemoryManager = OSCacheManager(self.reader, pin=self.pin_file)
+            self.memory_manager: MemoryManager = OSCacheManager(self.reader, pin=pin_file)
+            if self.pin_file:  # settled now: the size of the staging pool depends on it
+                self.memory_manager.open()
+                self.pin_file = self.memory_manager.pinned
         else:
             # schedule-driven read-ahead over the mapping (the reference's process cache role)
             md = self.reader.metadata
@@ -205,17 +213,20 @@ class Loader:
         self.first_traversal_order = self.next_traversal_order()
 
     # ---- resources shared by the epochs
-    def _context_for(self, device):
-        """One native context per device used by this loader; its slots are the loader's ring."""
+    def _context_for(self, device, pipeline=0):
+        """One native context per (device, image pipeline) of this loader; its slots are the
+        loader's ring.  Two image fields never share a context: a context's slot holds the staged
+        bytes and descriptors of exactly one batch of one field."""
         if not ch.cuda.is_available():
             raise RuntimeError("ffcv_b200 decodes images on the GPU and has no CPU fallback: "
                                "no CUDA device is visible")
         index = device.index if device is not None and device.index is not None else ch.cuda.current_device()
+        index = (index, int(pipeline))
         if index not in self._contexts:
             # With the file pinned the GPU fetches most bytes itself: a few staging threads carry
             # the CPU's share, more of them only slow the gather down (measured).
             threads = min(self.num_workers, 4) if self.pin_file else self.num_workers
-            self._contexts[index] = L.Context(index, n_slots=self.batches_ahead + 2, n_threads=threads)
+            self._contexts[index] = L.Context(index[0], n_slots=self.batches_ahead + 2, n_threads=threads)
             # the payload copy of a batch overlaps the drawing of the next batch's parameters
             self._contexts[index].set_async_staging(True)
             if self.pin_file:

@@ -53,11 +53,17 @@ class OSCacheManager(MemoryManager):
     """``pin=False``: the file is memory-mapped (page cache) and the native staging threads copy
     each batch's bytes into pinned buffers.  ``pin=True``: the whole file is read once into
     page-locked host memory; the native library notices that its source is pinned and lets the GPU
-    gather every batch's payloads over PCIe itself, so no CPU core touches sample bytes."""
+    gather every batch's payloads over PCIe itself, so no CPU core touches sample bytes.
+    ``pin='auto'``: a file on a memory file system is page-locked where it lies (one copy for
+    the node, nothing extra is allocated); any other file gets a private page-locked copy only
+    if the copies of all ranks of this host (``LOCAL_WORLD_SIZE``) together fit half of the
+    memory that is available now -- page-locked memory cannot be swapped, and eight ranks
+    copying a 40 GB file would lock 320 GB -- and is staged from the page cache otherwise."""
 
     def __init__(self, reader, pin=False):
         super().__init__(reader)
         self.mmap = None
+        self.auto = pin == 'auto'
         self.pin = bool(pin)
         self.pinned = False
         self._keepalive = None
@@ -68,9 +74,10 @@ class OSCacheManager(MemoryManager):
             if self.pin:
                 try:
                     self.mmap = self._register_shared()
-                    if self.mmap is None:
+                    if self.mmap is None and (not self.auto or self._private_copy_fits()):
                         self.mmap = self._read_pinned()
-                    self.pinned = True
+                    self.pinned = self.mmap is not None
+                    self.pin = self.pinned
                 except Exception as exc:  # not enough lockable memory, no CUDA: keep the staged path
                     print(f'ffcv_b200: could not pin {self.reader.file_name} ({exc}); using the page cache')
                     self.pin = False
@@ -78,11 +85,24 @@ class OSCacheManager(MemoryManager):
                 self.mmap = np.memmap(self.reader.file_name, 'uint8', mode='r')
         return self.mmap
 
+    def _private_copy_fits(self):
+        import os
+        ranks = max(1, int(os.environ.get('LOCAL_WORLD_SIZE', '1')))
+        need = os.path.getsize(self.reader.file_name) * ranks
+        try:
+            with open('/proc/meminfo') as fp:
+                avail = next(int(ln.split()[1]) * 1024 for ln in fp if ln.startswith('MemAvailable:'))
+        except (OSError, StopIteration, ValueError):
+            return False
+        return need <= avail // 2
+
     def _register_shared(self):
         """Page-locks the file's own pages in place: a shared, writable mapping of a file on a
         memory file system (``/dev/shm``) can be registered with the CUDA driver, which makes the
         page cache itself the pinned copy -- nothing is read at start-up and every process of the
-        node shares the one copy.  (Read-only mappings and files on disk are refused by the
+        node shares the one copy.  The driver only accepts a writable mapping, so the dataset file
+        is opened read-write (a file this user cannot write is not registered); this code never
+        stores through the mapping and hands out a read-only array.  (Read-only mappings and files on disk are refused by the
         driver; then the caller falls back to a private pinned copy.)  Nothing is ever written
         through the mapping.  Returns None when the file cannot be registered."""
         import mmap

@@ -94,7 +94,7 @@ class Graph:
     def collect_requirements(self):
         """Walks every pipeline root to leaf: ``accept_field``, ``accept_globals``,
         ``declare_state_and_memory`` (cf. ffcv/pipeline/graph.py:295-354), then fuses."""
-        for p in self.pipelines:
+        for pi, p in enumerate(self.pipelines):
             field = self.handlers[p.source]
             column = self.metadata[f'f{p.f_ix}']
             state = INITIAL_STATE
@@ -117,7 +117,7 @@ class Graph:
                     raise RuntimeError("image decoder refused to open a GPU plan")
                 p.n_fused = k
                 mm = self.memory_manager
-                p.executor = FusedImageExecutor(plan, self.context_factory(plan.device), column,
+                p.executor = FusedImageExecutor(plan, self.context_factory(plan.device, pi), column,
                                                 mm.sizes_of(column['data_ptr']), mm.file_base, self.seed)
             p.codes = [op.generate_code() for op in p.ops[p.n_fused:]]
         return self.pipelines

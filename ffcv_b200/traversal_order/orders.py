@@ -4,7 +4,9 @@
 ``DistributedSampler`` when ``distributed=True`` (a process group must exist).  ``QuasiRandom``
 keeps the reference's page-aware shuffle and, unlike the reference (which raises
 ``NotImplementedError``, quasi_random.py:54-56), also works distributed: every rank shuffles its
-strided share of the indices, which keeps the sharding collective-free.
+strided share of the indices, which keeps the sharding collective-free.  The index list is first
+padded with its own head to a multiple of the world size, as ``DistributedSampler`` does, so every
+rank sees the same number of samples and therefore the same number of batches.
 """
 from abc import ABC, abstractmethod
 from typing import Sequence
@@ -92,18 +94,23 @@ class QuasiRandom(TraversalOrder):
         if self.distributed:
             if not dist.is_initialized():
                 raise RuntimeError("distributed=True needs an initialised torch.distributed process group")
-            indices = indices[dist.get_rank()::dist.get_world_size()]
+            world = dist.get_world_size()
+            pad = (-len(indices)) % world
+            if pad and len(indices):
+                indices = np.concatenate([indices, np.resize(indices, pad)])
+            indices = indices[dist.get_rank()::world]
         self.my_indices = indices
-        index_set = set(int(i) for i in indices)
+        values, counts = np.unique(indices, return_counts=True)
+        multiplicity = dict(zip(values.tolist(), counts.tolist()))  # > 1 only for padded samples
         first_page = min(page_to_samples.keys())
         num_pages = max(page_to_samples.keys()) - first_page + 1
-        width = max(len(v) for v in page_to_samples.values())
+        width = max(len(v) for v in page_to_samples.values()) * (int(counts.max()) if len(counts) else 1)
         self.page_to_samples_array = np.zeros((num_pages, width), dtype=np.int64)
         self.page_sizes = np.zeros(num_pages, dtype=np.int64)
         for page, content in page_to_samples.items():
             row = page - first_page
             for c in sorted(content):
-                if c in index_set:
+                for _ in range(multiplicity.get(c, 0)):
                     self.page_to_samples_array[row, self.page_sizes[row]] = c
                     self.page_sizes[row] += 1
 

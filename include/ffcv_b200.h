@@ -251,6 +251,9 @@ int imdecode(unsigned char *input_buffer, uint64_t input_size, uint32_t source_h
              uint32_t scale_denom, bool enable_crop, bool hflip);
 /* libffcv/libffcv.cpp:44-46. */
 void my_memcpy(void *source, void *dst, uint64_t size);
+/* libffcv/libffcv.cpp:48-51: seek to `offset` in the C stream `fp` (a FILE * passed as an
+ * integer) and read `size` bytes into `destination`.  The reference's Python never binds it. */
+void my_fread(int64_t fp, int64_t offset, void *destination, int64_t size);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,6 @@
-"""Generates tests/golden/*.npz.  Run in a container that has /root/reference, cv2 and Pillow:
+"""Generates tests/golden/*.npz.  Needs a checkout of the reference (libffcv/ffcv), cv2 and Pillow:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py --reference <path of the ffcv checkout> [pixel]
 
 jpeg_cases.npz    JPEG streams written by cv2.imencode (the call the reference's writer makes,
                   ffcv/fields/rgb_image.py:26-34) with their pixels as decoded by real libjpeg-turbo
@@ -12,14 +12,14 @@ jpeg_cases.npz    JPEG streams written by cv2.imencode (the call the reference's
                   triangle ("fancy") upsampling.
 resize_cases.npz  inputs and outputs of cv2.resize(INTER_AREA), the call of libffcv.cpp:40-41.
 crop_cases.npz    crop boxes from the reference's own get_random_crop / get_center_crop
-                  (function source taken from /root/reference/ffcv/fields/rgb_image.py at
+                  (function source taken from ffcv/fields/rgb_image.py of the checkout at
                   generation time, run under numpy's legacy seeded stream).
 normalize_cases.npz lookup tables built by the reference's NormalizeImage expression
                   (ffcv/transforms/normalize.py:42-43).
 pixel_cases.npz   outputs of the reference's own RandomBrightness / RandomContrast /
                   RandomSaturation / ImageMixup / LabelMixup / Poison closures
                   (ffcv/transforms/color_jitter.py, mixup.py, poisoning.py), imported from
-                  /root/reference and compiled by the reference's Compiler with one thread (with
+                  the checkout and compiled by the reference's Compiler with one thread (with
                   more, numba parallelises even the per-batch random draws and the result is not
                   reproducible), numba's random stream seeded before each call; the draws
                   themselves (made by the same calls in the same order) are stored beside them.
@@ -38,7 +38,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import libjpeg_direct  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = '/root/reference/ffcv/fields/rgb_image.py'
+REF_ROOT = None  # set from --reference
 
 
 def smooth(rng, h, w):
@@ -113,6 +113,7 @@ def resize_cases():
 
 
 def reference_functions(names):
+    REF = os.path.join(REF_ROOT, 'ffcv', 'fields', 'rgb_image.py')
     tree = ast.parse(open(REF).read())
     ns = {'np': np}
     for node in tree.body:
@@ -162,7 +163,7 @@ def import_reference_transforms():
     import importlib
     import types
     pkg = types.ModuleType('ffcv')
-    pkg.__path__ = ['/root/reference/ffcv']
+    pkg.__path__ = [os.path.join(REF_ROOT, 'ffcv')]
     sys.modules['ffcv'] = pkg
     stub = types.ModuleType('ffcv.libffcv')
     stub.ctypes_resize = stub.imdecode = stub.memcpy = stub.resize_crop = None
@@ -260,7 +261,13 @@ def pixel_cases():
 
 
 if __name__ == '__main__':
-    if 'pixel' in sys.argv[1:]:
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--reference', required=True, help='root of the libffcv/ffcv checkout')
+    ap.add_argument('what', nargs='?', default='all', choices=['all', 'pixel'])
+    cli = ap.parse_args()
+    REF_ROOT = os.path.abspath(cli.reference)
+    if cli.what == 'pixel':
         pixel_cases()
         raise SystemExit
     jpeg_cases()

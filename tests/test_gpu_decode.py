@@ -103,3 +103,70 @@ def test_memcpy():
     b = np.zeros_like(a)
     memcpy(a, b)
     assert np.array_equal(a, b)
+
+
+# ---- the GPU against the third-party binaries themselves (no oracle in between) ----------------
+
+@pytest.mark.parametrize('case', CASES,
+                         ids=lambda c: f'{c[0]}x{c[1]}q{c[2]}s{c[3]}r{c[4]}o{c[5]}{c[6]}')
+def test_imdecode_against_libjpeg_turbo(case):
+    """`imdecode` on the GPU against libjpeg-turbo itself (Pillow's bundled binary, driven with
+    dct_method = JDCT_IFAST and fancy upsampling, the configuration the reference's
+    tjDecompress2(..., TJFLAG_FASTDCT) call selects, libffcv/libffcv.cpp:104-106): bit-exact."""
+    import libjpeg_direct
+    if not libjpeg_direct.available():
+        pytest.skip("Pillow's libjpeg-turbo binary is not present")
+    from ffcv_b200.libffcv import imdecode
+    h, w, q, samp, rst, opt, kind = case
+    rng = np.random.default_rng(h * 10007 + w)
+    buf = _encode(_content(rng, h, w, kind), q, samp, rst, opt)
+    want = libjpeg_direct.decode(buf, libjpeg_direct.JDCT_IFAST, True)
+    got = np.zeros((h, w, 3), dtype=np.uint8)
+    assert imdecode(buf, got, h, w, h, w, 0, 0, 1, 1, False, False) == 0
+    assert np.array_equal(got, want)
+
+
+def test_resize_crop_against_cv2_inter_area():
+    """`resize` on the GPU against cv2.resize(..., INTER_AREA) itself, the call of
+    libffcv/libffcv.cpp:40-41: bar 1 LSB, 0 asserted (all three regimes: integer factors,
+    fractional shrink, enlargement)."""
+    from ffcv_b200.libffcv import resize_crop
+    rng = np.random.default_rng(12)
+    shapes = [(224, 224), (160, 160), (256, 256), (32, 32), (7, 13), (384, 384)]
+    cases = []
+    for t in range(48):
+        H, W = int(rng.integers(8, 520)), int(rng.integers(8, 520))
+        h, w = int(rng.integers(1, H + 1)), int(rng.integers(1, W + 1))
+        cases.append((H, W, h, w) + shapes[t % 6])
+    for fy, fx in [(1, 1), (2, 2), (3, 3), (4, 4), (3, 2), (2, 3), (1, 2), (2, 1), (7, 7)]:
+        cases.append((fy * 32 + 5, fx * 48 + 7, fy * 32, fx * 48, 32, 48))
+    cases.append((1300, 1700, 1201, 1577, 384, 384))
+    for H, W, h, w, dh, dw in cases:
+        src = rng.integers(0, 256, (H, W, 3), dtype=np.uint8)
+        r0, c0 = int(rng.integers(0, H - h + 1)), int(rng.integers(0, W - w + 1))
+        want = cv2.resize(src[r0:r0 + h, c0:c0 + w], (dw, dh), interpolation=cv2.INTER_AREA)
+        got = np.zeros((dh, dw, 3), dtype=np.uint8)
+        resize_crop(src, r0, r0 + h, c0, c0 + w, got)
+        diff = np.abs(got.astype(int) - want.astype(int))
+        assert diff.max() == 0, (H, W, h, w, dh, dw, int(diff.max()), int((diff > 0).sum()))
+
+
+def test_my_fread(tmp_path):
+    """`my_fread(FILE *, offset, dst, size)` (libffcv/libffcv.cpp:48-51) through a C stream."""
+    import ctypes
+    from ffcv_b200.libffcv import lib
+    libc = ctypes.CDLL(None)
+    libc.fopen.restype = ctypes.c_void_p
+    libc.fopen.argtypes = [ctypes.c_char_p, ctypes.c_char_p]
+    libc.fclose.argtypes = [ctypes.c_void_p]
+    data = np.random.default_rng(5).integers(0, 256, 10000, dtype=np.uint8)
+    path = tmp_path / 'blob.bin'
+    data.tofile(str(path))
+    fp = libc.fopen(str(path).encode(), b'rb')
+    assert fp
+    lib.my_fread.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64]
+    lib.my_fread.restype = None
+    out = np.zeros(777, dtype=np.uint8)
+    lib.my_fread(fp, 1234, out.ctypes.data, out.size)
+    libc.fclose(fp)
+    assert np.array_equal(out, data[1234:1234 + 777])

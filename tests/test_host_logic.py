@@ -15,9 +15,9 @@ def test_library_exports_every_declared_symbol():
     from ffcv_b200 import libffcv
     header = open(os.path.join(ROOT, 'include', 'ffcv_b200.h')).read()
     header = re.sub(r'/\*.*?\*/', '', header, flags=re.S)
-    names = set(re.findall(r'\b(ffcvb_\w+|imdecode|resize|my_memcpy)\s*\(', header))
+    names = set(re.findall(r'\b(ffcvb_\w+|imdecode|resize|my_memcpy|my_fread)\s*\(', header))
     assert {'ffcvb_create', 'ffcvb_stage_batch', 'ffcvb_submit_batch', 'ffcvb_transform_device', 'imdecode',
-            'resize', 'my_memcpy'} <= names
+            'resize', 'my_memcpy', 'my_fread'} <= names
     for n in names:
         assert hasattr(libffcv.lib, n), f'{n} declared in include/ffcv_b200.h but not exported'
 

@@ -3,12 +3,14 @@
 It serves callers that may not allocate GPU memory while running (all device memory already
 belongs to their own pool, or an allocation's device-wide synchronisation is unaffordable), so its
 scratch is a fixed array inside the library.  Checked here through the C ABI against the regular
-`imdecode` entry point: identical pixels, on two calls in a row that share the scratch (a large
-image first, then a small one, then the large one again), plus the refusal of inputs beyond the
-fixed limits.  The buffers the *caller* passes are allocated by the test with torch."""
+`imdecode` entry point and against the CPU oracle: identical pixels, on two calls in a row that
+share the scratch (a large image first, then a small one, then the large one again), plus the
+refusal of inputs beyond the fixed limits.  The buffers the *caller* passes are allocated by the test with torch."""
 import cv2
 import numpy as np
 import pytest
+
+from parity import O
 
 pytestmark = pytest.mark.gpu
 
@@ -49,6 +51,7 @@ def test_static_decode_matches_imdecode_on_consecutive_calls():
                         (small, (61, 83))]:
         got, want = _decode_both(buf, h, w)
         assert np.array_equal(got, want)
+        assert np.array_equal(got, O.jpeg_decode(buf))  # and not merely equal to each other
 
 
 def test_static_decode_refuses_what_does_not_fit():
