@@ -185,6 +185,15 @@ struct Slot {
     bool copy_done = true; // the staging threads have finished this slot's payload copy (guarded by ctx->copy_m)
     std::vector<ImageDesc> descs;
     std::vector<uint64_t> src_ptrs;
+    // values of the sample's other fields that travel in the head of this batch's blob
+    struct Rider {
+        std::vector<uint8_t> inline_bytes; // n * item_bytes, or empty when gathered from the file
+        std::vector<uint64_t> ptrs;        // file offsets of the n items (gathered riders)
+        uint64_t item_bytes = 0;
+        void *dst_dev = nullptr;
+        uint64_t off = 0, bytes = 0;       // place in the blob (set by ffcvb_stage_batch)
+    };
+    std::vector<Rider> pending_riders, riders; // set for the next staging / staged with the current batch
     double stage_ms[4] = {0, 0, 0, 0}; // header parse, layout, payload copy, total
     std::vector<JpegHeader> headers;
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -645,6 +654,19 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     off = align_up(off + sizeof(MultTable) * mult_src.size(), 16);
     hd.params_off = off;
     off = align_up(off + sizeof(int32_t) * (size_t)n * n_params, 16);
+    s.riders.swap(s.pending_riders);
+    s.pending_riders.clear();
+    for (auto &r : s.riders) {
+        r.bytes = r.item_bytes * (uint64_t)n;
+        if ((!r.inline_bytes.empty() && r.inline_bytes.size() != r.bytes) ||
+            (r.inline_bytes.empty() && r.ptrs.size() != (size_t)n)) {
+            s.riders.clear();
+            return fail(ctx, FFCVB_E_ARG, "ffcvb_stage_batch: a rider was set for a different number of samples");
+        }
+        r.off = off = align_up(off, 64);
+        off += r.bytes;
+    }
+    off = align_up(off, 16);
     s.jpeg_list_off = off;
     off = align_up(off + sizeof(int32_t) * jpeg_list.size(), 16);
     s.par_list_off = off;
@@ -697,6 +719,14 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     for (size_t k = 0; k < mult_src.size(); k++)
         build_mult_table(mult_src[k], reinterpret_cast<MultTable *>(s.host + hd.mult_off) + k);
     memcpy(s.host + hd.params_off, params, sizeof(int32_t) * (size_t)n * n_params);
+    for (const auto &r : s.riders) {
+        if (!r.inline_bytes.empty()) {
+            memcpy(s.host + r.off, r.inline_bytes.data(), r.bytes);
+        } else {
+            for (int i = 0; i < n; i++)
+                memcpy(s.host + r.off + (size_t)i * r.item_bytes, file_base + r.ptrs[i], r.item_bytes);
+        }
+    }
     if (!jpeg_list.empty()) memcpy(s.host + s.jpeg_list_off, jpeg_list.data(), 4 * jpeg_list.size());
     if (!par_list.empty()) memcpy(s.host + s.par_list_off, par_list.data(), 4 * par_list.size());
     if (!seq_list.empty()) memcpy(s.host + s.seq_list_off, seq_list.data(), 4 * seq_list.size());
@@ -841,6 +871,9 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         }
         CU(cudaStreamWaitEvent(st, s.ev_gathered, 0));
     }
+    if (copy)
+        for (const auto &r : s.riders)
+            if (r.bytes) CU(cudaMemcpyAsync(r.dst_dev, blob + r.off, r.bytes, cudaMemcpyDeviceToDevice, st));
     if (prof) CU(cudaEventRecord(s.ev[1], st));
     const ImageDesc *descs = reinterpret_cast<const ImageDesc *>(blob + hd.desc_off);
     const HuffTable *huff = reinterpret_cast<const HuffTable *>(blob + hd.huff_off);
@@ -875,6 +908,34 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
     if (prof) {
         CU(cudaEventRecord(s.ev[5], st));
         s.timed = true;
+    }
+    return FFCVB_OK;
+}
+
+int ffcvb_set_batch_riders(ffcvb_ctx *ctx, int slot, const ffcvb_rider *riders, int n_riders, int n) {
+    if (!ctx) return FFCVB_E_ARG;
+    if (slot < 0 || slot >= (int)ctx->slots.size() || n_riders < 0 || n_riders > FFCVB_MAX_RIDERS || n <= 0 ||
+        (n_riders > 0 && !riders))
+        return fail(ctx, FFCVB_E_ARG, "ffcvb_set_batch_riders: bad argument");
+    Slot &s = ctx->slots[slot];
+    s.pending_riders.clear();
+    for (int k = 0; k < n_riders; k++) {
+        const ffcvb_rider &in = riders[k];
+        if (!in.dst_dev || in.item_bytes == 0 || in.item_bytes > (1u << 24) || (!in.host == !in.ptrs)) {
+            s.pending_riders.clear();
+            return fail(ctx, FFCVB_E_ARG, "ffcvb_set_batch_riders: rider %d needs a destination, an item size and "
+                                          "exactly one of host / ptrs", k);
+        }
+        Slot::Rider r;
+        r.item_bytes = in.item_bytes;
+        r.dst_dev = in.dst_dev;
+        if (in.host) {
+            const uint8_t *b = static_cast<const uint8_t *>(in.host);
+            r.inline_bytes.assign(b, b + (size_t)n * in.item_bytes);
+        } else {
+            r.ptrs.assign(in.ptrs, in.ptrs + n);
+        }
+        s.pending_riders.push_back(std::move(r));
     }
     return FFCVB_OK;
 }

@@ -37,6 +37,14 @@ class Plan(Structure):
                 ('n_ops', c_int32), ('ops', Op * MAX_OPS), ('lut_dev', c_void_p)]
 
 
+class Rider(Structure):
+    _fields_ = [('host', c_void_p), ('ptrs', c_void_p), ('item_bytes', c_uint64), ('dst_dev', c_void_p)]
+
+
+MAX_RIDERS = 8
+
+lib.ffcvb_set_batch_riders.argtypes = [c_void_p, c_int, POINTER(Rider), c_int, c_int]
+lib.ffcvb_set_batch_riders.restype = c_int
 lib.ffcvb_create.argtypes = [c_int, c_int, c_int, POINTER(c_void_p)]
 lib.ffcvb_create.restype = c_int
 lib.ffcvb_destroy.argtypes = [c_void_p]
@@ -170,6 +178,27 @@ class Context:
                                    modes.ctypes.data, heights.ctypes.data, widths.ctypes.data, n,
                                    ctypes.byref(plan), params.ctypes.data)
         self._check(rc, 'ffcvb_stage_batch')
+
+    def set_riders(self, slot, riders, n):
+        """riders: sequence of (values, file_offsets, item_bytes, dst_ptr) -- exactly one of
+        `values` (contiguous numpy array of n items) and `file_offsets` (uint64 array of n offsets
+        from the file base given to stage) is not None.  Consumed by the next `stage` of the slot."""
+        arr = (Rider * max(1, len(riders)))()
+        keep = []
+        for k, (values, offsets, item_bytes, dst_ptr) in enumerate(riders):
+            if values is not None:
+                values = np.ascontiguousarray(values)
+                assert values.nbytes == n * item_bytes, (values.nbytes, n, item_bytes)
+                arr[k].host, arr[k].ptrs = values.ctypes.data, None
+                keep.append(values)
+            else:
+                offsets = _as(offsets, np.uint64)
+                assert offsets.shape == (n,)
+                arr[k].host, arr[k].ptrs = None, offsets.ctypes.data
+                keep.append(offsets)
+            arr[k].item_bytes = int(item_bytes)
+            arr[k].dst_dev = int(dst_ptr)
+        self._check(lib.ffcvb_set_batch_riders(self._h, slot, arr, len(riders), int(n)), 'ffcvb_set_batch_riders')
 
     def submit(self, slot, stream, out_ptr):
         self._check(lib.ffcvb_submit_batch(self._h, slot, stream or None, out_ptr), 'ffcvb_submit_batch')

@@ -125,6 +125,7 @@ class FusedImageExecutor:
         self.param_log = None     # set to a list to record (epoch, batch, indices, parameter table) per batch
         self.h2d_bytes = 0
         self.launches = 0
+        self.riders = []          # other fields' values for the next batch (see Graph.attach_riders)
 
     def allocate(self, batch_size, slots):
         p = self.plan
@@ -165,6 +166,9 @@ class FusedImageExecutor:
         if self.param_log is not None:
             self.param_log.append((epoch, batch_ix, np.array(batch_indices), params.copy()))
         n = len(batch_indices)
+        if self.riders:
+            self.ctx.set_riders(slot, self.riders, n)
+            self.riders = []
         # with asynchronous staging this returns while the staging threads still copy the payloads ...
         self.ctx.stage(slot, self.file_base_fn(), *args[:5], self.native_plan, params)
         # ... which is when the next batch's parameters are drawn

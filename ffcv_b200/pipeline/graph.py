@@ -13,6 +13,8 @@ import numpy as np
 import torch as ch
 
 from .. import libffcv as L
+from ..fields.basics import FloatDecoder, IntDecoder
+from ..fields.ndarray import NDArrayDecoder
 from ..fields.rgb_image import SimpleRGBImageDecoder
 from .allocation_query import AllocationQuery, allocate_query
 from .fusion import FusedImageExecutor, FusedImagePlan
@@ -67,6 +69,7 @@ class _Pipeline:
         self.n_fused = 0
         self.codes = []
         self.final_state = None
+        self.rider_host = None  # index of the image pipeline whose staged bytes carry this field
 
 
 class Graph:
@@ -119,14 +122,53 @@ class Graph:
                 mm = self.memory_manager
                 p.executor = FusedImageExecutor(plan, self.context_factory(plan.device, pi), column,
                                                 mm.sizes_of(column['data_ptr']), mm.file_base, self.seed)
+        self.attach_riders()
+        for p in self.pipelines:
             p.codes = [op.generate_code() for op in p.ops[p.n_fused:]]
         return self.pipelines
+
+    def attach_riders(self):
+        """A scalar or fixed-shape array field whose pipeline opens with ``decoder -> ToTensor ->
+        ToDevice(gpu)`` does not get a host buffer and a copy of its own
+        (ffcv/fields/basics.py:28-34, ffcv/fields/ndarray.py:37-43, ffcv/transforms/ops.py:50-57):
+        its values ride in the staged bytes of an image pipeline decoded on that GPU and arrive
+        with the same host->device transfer.  The rest of its pipeline runs unchanged on the
+        device tensor."""
+        from ..transforms.ops import ToDevice, ToTensor
+        hosts = {}
+        for pi, p in enumerate(self.pipelines):
+            if p.executor is not None:
+                hosts.setdefault(p.executor.device, []).append(pi)
+        for p in self.pipelines:
+            p.rider_host = None
+        if not hosts:
+            return
+        load = {pi: 0 for pis in hosts.values() for pi in pis}
+        for p in self.pipelines:
+            p.rider_host = None
+            if p.executor is not None or len(p.ops) < 3:
+                continue
+            dec, to_tensor, to_device = p.ops[:3]
+            if type(dec) not in (IntDecoder, FloatDecoder, NDArrayDecoder) or type(to_tensor) is not ToTensor \
+                    or type(to_device) is not ToDevice or to_device.device.type != 'cuda':
+                continue
+            dev = to_device.device
+            if dev.index is None:
+                dev = ch.device('cuda', ch.cuda.current_device())
+            cands = [pi for pi in hosts.get(dev, []) if load[pi] < L.MAX_RIDERS]
+            if not cands:
+                continue
+            p.rider_host = cands[0]
+            load[cands[0]] += 1
+            p.n_fused = 3
 
     def allocate_memory(self, batch_size, slots):
         buffers = {}
         for pi, p in enumerate(self.pipelines):
             if p.executor is not None:
                 buffers[(pi, 'fused')] = p.executor.allocate(batch_size, slots)
+            if p.rider_host is not None:
+                buffers[(pi, 'rider')] = allocate_query(p.allocs[2], batch_size, slots)
             for k in range(p.n_fused, len(p.ops)):
                 alloc = p.allocs[k]
                 if isinstance(alloc, AllocationQuery):
@@ -150,7 +192,19 @@ class Graph:
         n = len(batch_indices)
         results = []
         for pi, p in enumerate(self.pipelines):
-            if p.executor is not None:
+            if p.rider_host is not None:  # queued before the image pipeline stages its batch
+                dst = buffers[(pi, 'rider')][slot][:n]
+                values = np.ascontiguousarray(self.metadata[f'f{p.f_ix}'][batch_indices])
+                if isinstance(p.ops[0], NDArrayDecoder):
+                    rider = (None, values.astype(np.uint64), int(p.ops[0].field.element_size), dst.data_ptr())
+                else:
+                    rider = (values, None, values.dtype.itemsize, dst.data_ptr())
+                self.pipelines[p.rider_host].executor.riders.append(rider)
+        for pi, p in enumerate(self.pipelines):
+            if p.rider_host is not None:
+                value = buffers[(pi, 'rider')][slot][:n]
+                first = p.n_fused
+            elif p.executor is not None:
                 value = p.executor(batch_indices, slot, stream_ptr, buffers[(pi, 'fused')][slot], epoch, batch_ix,
                                    lookahead=lookahead)
                 first = p.n_fused

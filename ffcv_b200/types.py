@@ -19,8 +19,8 @@ ARG_TYPE = np.dtype([('', '<u1', 1024)])
 
 
 def type_id_table():
-    from .fields import FloatField, IntField, RGBImageField
-    return {0: FloatField, 1: IntField, 2: RGBImageField, 255: None}
+    from .fields import FloatField, IntField, NDArrayField, RGBImageField, TorchTensorField
+    return {0: FloatField, 1: IntField, 2: RGBImageField, 4: NDArrayField, 6: TorchTensorField, 255: None}
 
 
 def get_metadata_type(handlers):

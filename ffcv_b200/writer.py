@@ -117,7 +117,11 @@ class DatasetWriter:
                     ptr = data_start + page_ix * self.page_size + page_off
                     page[page_off:page_off + size] = storage
                     page_off += size
-                    metadata[lo + k][f'f{f_ix}']['data_ptr'] = ptr
+                    column = metadata[f'f{f_ix}']
+                    if column.dtype.names:  # image fields keep the pointer beside mode and size
+                        column['data_ptr'][lo + k] = ptr
+                    else:                   # array fields: the pointer is the whole entry
+                        column[lo + k] = ptr
                     allocs.append((lo + k, ptr, size))
 
             if self.num_workers > 1 and len(chunks) > 1:

@@ -106,6 +106,25 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                       const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
                       const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params);
 
+/* Riders: values of the samples' other fields that travel inside the image batch's staged bytes, so
+ * that a whole batch (pixels, labels, small arrays) is one host->device transfer.  Replaces the
+ * separate per-batch copy that IntDecoder / FloatDecoder / NDArrayDecoder followed by ToTensor and
+ * ToDevice cause in the reference (ffcv/fields/basics.py:28-34, ffcv/fields/ndarray.py:37-43,
+ * ffcv/transforms/ops.py:50-57).  Call before ffcvb_stage_batch of the same slot with the same
+ * `n`; the next ffcvb_stage_batch consumes the riders (they are not kept for later batches).
+ * A rider is `n` items of `item_bytes` each: either `host` (contiguous values, copied by this call)
+ * or `ptrs` (n offsets from ffcvb_stage_batch's `file_base`, read when the batch is staged).
+ * ffcvb_submit_batch then copies the n * item_bytes bytes, device to device on its stream, into
+ * `dst_dev`, a DEVICE buffer of the caller. */
+#define FFCVB_MAX_RIDERS 8
+typedef struct {
+    const void *host;     /* n * item_bytes contiguous bytes, or NULL */
+    const uint64_t *ptrs; /* n file offsets, or NULL (exactly one of host / ptrs) */
+    uint64_t item_bytes;
+    void *dst_dev;
+} ffcvb_rider;
+int ffcvb_set_batch_riders(ffcvb_ctx *ctx, int slot, const ffcvb_rider *riders, int n_riders, int n);
+
 /* With asynchronous staging enabled, ffcvb_stage_batch returns as soon as the batch is laid out
  * and leaves the payload copy running on the staging threads.  ffcvb_submit_batch of that slot
  * does not wait for it either: it queues a stream callback that holds `stream` until the copy is

@@ -277,3 +277,110 @@ def test_file_on_memory_file_system_is_pinned_in_place(tmp_path):
             del loader
     finally:
         os.remove(shm)
+
+
+# ---- full-size batches, fixed-size JPEG datasets, several fields per sample ---------------------
+
+@pytest.mark.parametrize('cfg,batch,res', [(2, 512, 224), (1, 1024, 160)])
+def test_full_size_batches(tmp_path, cfg, batch, res):
+    """One batch of the configuration's real size (512 x config 2, 1024 x config 1): the CTA sizes,
+    subsequence lengths and grid shapes the benchmark runs with, checked against the oracle."""
+    from ffcv_b200 import OrderOption
+    from ffcv_b200.fields.decoders import RandomResizedCropRGBImageDecoder
+    from ffcv_b200.synthetic import write_dataset_isolated as write_dataset
+    from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, ToTorchImage
+    path = write_dataset(cfg, str(tmp_path / f'c{cfg}_{batch}.beton'), batch, num_workers=8)
+    pipes = {'image': [RandomResizedCropRGBImageDecoder((res, res)), RandomHorizontalFlip(),
+                       NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()],
+             'label': None}
+    loader = _loader(path, batch, pipes, order=OrderOption.QUASI_RANDOM)
+    assert compare_epoch(loader) == batch * res * res * 3
+    status = image_executor(loader).ctx.status(0, ch.cuda.current_stream().cuda_stream, batch)
+    assert (status == 0).all()
+
+
+class _ManyFields:
+    """(image, label, vector, weight, second image) samples with seeded content."""
+
+    def __init__(self, n, h, w):
+        self.n, self.h, self.w = n, h, w
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, k):
+        from ffcv_b200.synthetic import synth_content
+        rng = np.random.default_rng([77, k])
+        np.random.seed(k)
+        return (synth_content(rng, self.h, self.w), int(rng.integers(0, 1000)),
+                rng.standard_normal((5, 3)).astype(np.float32), float(rng.uniform()),
+                synth_content(rng, self.h // 2, self.w // 2))
+
+
+def _write_many_fields(path, n, h, w):
+    """In a fresh interpreter: the writer forks, which a process that runs CUDA must not do."""
+    import subprocess
+    import sys
+    code = ('import sys; sys.path[:0] = [%r, %r]; import numpy as np\n'
+            'from test_gpu_pipeline import _ManyFields\n'
+            'from ffcv_b200.fields import RGBImageField, IntField, NDArrayField, FloatField\n'
+            'from ffcv_b200.writer import DatasetWriter\n'
+            'DatasetWriter(%r, {"image": RGBImageField(write_mode="jpg"), "label": IntField(), '
+            '"vec": NDArrayField(np.dtype("float32"), (5, 3)), "weight": FloatField(), '
+            '"mask": RGBImageField(write_mode="proportion")}, num_workers=4).from_indexed_dataset(_ManyFields(%d, %d, %d))\n'
+            % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.path.dirname(os.path.abspath(__file__)),
+               path, n, h, w))
+    subprocess.run([sys.executable, '-c', code], check=True, env=dict(os.environ, CUDA_VISIBLE_DEVICES=''))
+    return path
+
+
+def test_fixed_size_jpeg_labels_arrays_and_two_image_fields(tmp_path):
+    """A fixed-size all-JPEG field through SimpleRGBImageDecoder; labels, a float field and an
+    array field that ride in the image batch's staged bytes (one host->device transfer per batch);
+    and a second image field, which must get a context of its own."""
+    from ffcv_b200.fields.decoders import (FloatDecoder, IntDecoder, NDArrayDecoder, RandomResizedCropRGBImageDecoder,
+                                           SimpleRGBImageDecoder)
+    from ffcv_b200.reader import Reader
+    from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, Squeeze, ToDevice, ToTensor, ToTorchImage
+    n, h, w = 96, 72, 104
+    path = _write_many_fields(str(tmp_path / 'many.beton'), n, h, w)
+    dev = ch.device('cuda:0')
+    pipes = {
+        'image': [SimpleRGBImageDecoder(), RandomHorizontalFlip(), ToTensor(), ToDevice(dev), ToTorchImage(),
+                  NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16)],
+        'label': [IntDecoder(), ToTensor(), ToDevice(dev), Squeeze()],
+        'vec': [NDArrayDecoder(), ToTensor(), ToDevice(dev)],
+        'weight': [FloatDecoder(), ToTensor(), ToDevice(dev)],
+        'mask': [RandomResizedCropRGBImageDecoder((40, 40)), ToTensor(), ToDevice(dev), ToTorchImage()],
+    }
+    loader = _loader(path, 32, pipes)
+    g = loader.graph
+    by_name = {p.name: p for p in g.pipelines}
+    assert all(by_name[k].rider_host is not None for k in ('label', 'vec', 'weight'))
+    assert by_name['image'].executor.ctx is not by_name['mask'].executor.ctx
+    r = Reader(path)
+    mm = loader.memory_manager.open()
+    truth_vec = np.stack([np.frombuffer(mm[int(p):int(p) + 60].tobytes(), np.float32).reshape(5, 3)
+                          for p in r.metadata['f2']])
+    labels, vecs, weights = [], [], []
+    for batch in loader:
+        assert all(t.device == dev for t in batch)
+        labels.append(batch[1].clone())
+        vecs.append(batch[2].clone())
+        weights.append(batch[3].clone())
+    assert labels[0].shape == (32,) and vecs[0].shape == (32, 5, 3) and weights[0].shape == (32, 1)
+    assert np.array_equal(ch.cat(labels).cpu().numpy(), r.metadata['f1'])
+    assert np.array_equal(ch.cat(vecs).cpu().numpy(), truth_vec)
+    assert np.array_equal(ch.cat(weights).cpu().numpy().ravel(), r.metadata['f3'])
+    # the riders add their bytes to the image batch's one transfer and nothing else is copied
+    # (one batch per epoch, so that both loaders have staged the same samples when asked)
+    full = _loader(path, n, pipes)
+    bare = _loader(path, n, {'image': pipes['image'], 'label': None, 'vec': None, 'weight': None, 'mask': None})
+    for ld in (full, bare):
+        for _ in ld:
+            pass
+    extra = image_executor(full).h2d_bytes - image_executor(bare).h2d_bytes
+    assert n * (8 + 60 + 8) <= extra <= n * (8 + 60 + 8) + 4 * 64
+    # pixels of both image fields against the oracle (fresh loaders: every epoch redraws)
+    assert compare_epoch(_loader(path, 32, pipes), field_pos=0, field='image') == n * h * w * 3
+    assert compare_epoch(_loader(path, 32, pipes), field_pos=4, field='mask') == n * 40 * 40 * 3

@@ -189,3 +189,40 @@ def test_read_ahead_manager_follows_the_schedule(beton):
         if c[2] == os.POSIX_FADV_WILLNEED:
             first_want.setdefault(c[:2], k)
     assert all(first_want.get(c[:2], -1) < k for k, c in enumerate(calls) if c[2] == os.POSIX_FADV_DONTNEED)
+
+
+def test_ndarray_field_round_trip(tmp_path):
+    """NDArrayField / TorchTensorField: same field arguments and stored bytes as the reference
+    (ffcv/fields/ndarray.py), read back through the default pipeline on the host."""
+    from ffcv_b200 import Loader
+    from ffcv_b200.fields import FloatField, IntField, NDArrayField, TorchTensorField
+    from ffcv_b200.reader import Reader
+    from ffcv_b200.writer import DatasetWriter
+
+    rng = np.random.default_rng(4)
+    vec = rng.standard_normal((37, 3, 5)).astype(np.float32)
+    ten = rng.integers(-1000, 1000, (37, 4)).astype(np.int16)
+
+    class DS:
+        def __len__(self):
+            return 37
+
+        def __getitem__(self, i):
+            return vec[i], i * 3, float(i) / 7, ch.from_numpy(ten[i])
+
+    path = str(tmp_path / 'nd.beton')
+    DatasetWriter(path, {'vec': NDArrayField(np.dtype('float32'), (3, 5)), 'label': IntField(),
+                         'weight': FloatField(), 'ten': TorchTensorField(ch.int16, (4,))},
+                  num_workers=1).from_indexed_dataset(DS())
+    r = Reader(path)
+    assert type(r.handlers['vec']).__name__ == 'NDArrayField' and r.handlers['vec'].shape == (3, 5)
+    assert r.handlers['vec'].dtype == np.float32 and r.handlers['ten'].dtype == np.int16
+    assert [int(d['type_id']) for d in r.field_descriptors] == [4, 1, 0, 6]
+    loader = Loader(path, batch_size=16, num_workers=1, drop_last=False)
+    got = [[x.clone() for x in b] for b in loader]
+    assert np.array_equal(ch.cat([g[0] for g in got]).numpy(), vec)
+    assert np.array_equal(ch.cat([g[1] for g in got]).numpy().ravel(), np.arange(37) * 3)
+    assert np.allclose(ch.cat([g[2] for g in got]).numpy().ravel(), np.arange(37) / 7)
+    assert np.array_equal(ch.cat([g[3] for g in got]).numpy(), ten)
+    with pytest.raises(ValueError):
+        Loader(path, batch_size=16, batches_ahead=0)
