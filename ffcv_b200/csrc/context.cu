@@ -1010,6 +1010,18 @@ int ffcvb_stage_times(const ffcvb_ctx *ctx, int slot, double *ms) {
     return FFCVB_OK;
 }
 
+int ffcvb_gather_time(ffcvb_ctx *ctx, int slot, float *ms) {
+    if (!ctx) return FFCVB_E_ARG;
+    if (!ms || slot < 0 || slot >= (int)ctx->slots.size()) return fail(ctx, FFCVB_E_ARG, "ffcvb_gather_time: bad argument");
+    Slot &s = ctx->slots[slot];
+    *ms = -1.0f;
+    if (!s.gather_timed) return FFCVB_OK; // this slot's last batch was not gathered by the GPU
+    CU(cudaSetDevice(ctx->device));
+    CU(cudaEventSynchronize(s.ev_gathered));
+    CU(cudaEventElapsedTime(ms, s.ev_gather_start, s.ev_gathered));
+    return FFCVB_OK;
+}
+
 int ffcvb_batch_info(const ffcvb_ctx *ctx, int slot, int64_t *info) {
     if (!ctx || !info || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return FFCVB_E_ARG;
     const Slot &s = ctx->slots[slot];

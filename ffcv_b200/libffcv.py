@@ -85,6 +85,8 @@ lib.ffcvb_stage_times.argtypes = [c_void_p, c_int, c_void_p]
 lib.ffcvb_stage_times.restype = c_int
 lib.ffcvb_batch_info.argtypes = [c_void_p, c_int, c_void_p]
 lib.ffcvb_batch_info.restype = c_int
+lib.ffcvb_gather_time.argtypes = [c_void_p, c_int, c_void_p]
+lib.ffcvb_gather_time.restype = c_int
 lib.ffcvb_batch_launches.argtypes = [c_void_p, c_int]
 lib.ffcvb_batch_launches.restype = c_int
 lib.ffcvb_batch_status.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int]
@@ -256,6 +258,12 @@ class Context:
         self._check(lib.ffcvb_batch_info(self._h, slot, info.ctypes.data), 'ffcvb_batch_info')
         keys = ('n', 'n_jpeg', 'blocks', 'scan_bytes', 'plane_bytes', 'rgb_bytes', 'raw_bytes', 'jpeg_bytes')
         return dict(zip(keys, (int(v) for v in info)))
+
+    def gather_time(self, slot):
+        """Milliseconds of the GPU's payload gather of the slot's last batch, or None."""
+        ms = ctypes.c_float(-1.0)
+        self._check(lib.ffcvb_gather_time(self._h, slot, ctypes.byref(ms)), 'ffcvb_gather_time')
+        return float(ms.value) if ms.value >= 0 else None
 
     def launches(self, slot):
         return int(lib.ffcvb_batch_launches(self._h, slot))

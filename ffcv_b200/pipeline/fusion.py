@@ -100,6 +100,37 @@ class FusedImagePlan:
         return self.torch_image and not self.channels_last and self.table is None
 
 
+def host_plan(ops, field, metadata):
+    """The :class:`FusedImagePlan` of the longest fusable prefix of ``ops`` (decoder first), built
+    on the host alone: no native context, no GPU.  ``metadata`` is the field's metadata column."""
+    plan = FusedImagePlan()
+    for op in ops:
+        op.accept_field(field)
+        op.accept_globals(metadata, None)
+        if not op.fuse(plan):
+            break
+        plan.fused_ops.append(op)
+    return plan
+
+
+def sample_plan_params(plan, md, base_seed, epoch, batch_ix):
+    """Parameter table of one batch, ``[n, 4 + 2 * len(plan.ops)]`` int32: the crop box of every
+    sample followed by the two values each augmentation draws.  ``md``: the batch's metadata rows.
+    Every operation seeds its own stream from (seed, epoch, batch, position in the pipeline)."""
+    heights = np.ascontiguousarray(md['height'])
+    widths = np.ascontiguousarray(md['width'])
+    n = len(md)
+    params = np.zeros((n, 4 + 2 * len(plan.ops)), dtype=np.int32)
+    crops = np.zeros((n, 4), dtype=np.int32)
+    (plan.crop_sampler or plan.decoder).sample_crops(batch_seed(base_seed, epoch, batch_ix, 0), heights, widths, crops)
+    params[:, :4] = crops
+    for k, (_, _, _, op) in enumerate(plan.ops):
+        col = np.zeros((n, 2), dtype=np.int32)
+        op.sample_params(batch_seed(base_seed, epoch, batch_ix, k + 1), n, plan.out_h, plan.out_w, col)
+        params[:, 4 + 2 * k:6 + 2 * k] = col
+    return params
+
+
 class FusedImageExecutor:
     """Per-batch driver of a :class:`FusedImagePlan` on one native context."""
 
@@ -132,20 +163,9 @@ class FusedImageExecutor:
         return [ch.empty((batch_size,) + p.buffer_shape, dtype=p.torch_dtype, device=self.device) for _ in range(slots)]
 
     def sample_params(self, batch_indices, epoch, batch_ix):
-        p = self.plan
         md = self.metadata[batch_indices]
-        heights = np.ascontiguousarray(md['height'])
-        widths = np.ascontiguousarray(md['width'])
-        n = len(batch_indices)
-        params = np.zeros((n, self.n_params), dtype=np.int32)
-        crops = np.zeros((n, 4), dtype=np.int32)
-        (p.crop_sampler or p.decoder).sample_crops(batch_seed(self.base_seed, epoch, batch_ix, 0), heights, widths, crops)
-        params[:, :4] = crops
-        for k, (_, _, _, op) in enumerate(p.ops):
-            col = np.zeros((n, 2), dtype=np.int32)
-            op.sample_params(batch_seed(self.base_seed, epoch, batch_ix, k + 1), n, p.out_h, p.out_w, col)
-            params[:, 4 + 2 * k:6 + 2 * k] = col
-        return md, heights, widths, params
+        params = sample_plan_params(self.plan, md, self.base_seed, epoch, batch_ix)
+        return md, np.ascontiguousarray(md['height']), np.ascontiguousarray(md['width']), params
 
     def prepare(self, batch_indices, epoch, batch_ix):
         """Everything ffcvb_stage_batch needs for one batch, as contiguous arrays."""

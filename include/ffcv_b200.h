@@ -188,6 +188,9 @@ int ffcvb_stage_times(const ffcvb_ctx *ctx, int slot, double *ms);
  * [6] staged raw-pixel bytes, [7] staged JPEG bytes. */
 int ffcvb_batch_info(const ffcvb_ctx *ctx, int slot, int64_t *info);
 int ffcvb_batch_launches(const ffcvb_ctx *ctx, int slot);
+/* Milliseconds the GPU's payload gather of the slot's last submitted batch took (waits for it);
+ * -1 when that batch was not gathered by the GPU.  No counterpart in the reference. */
+int ffcvb_gather_time(ffcvb_ctx *ctx, int slot, float *ms);
 
 /* After the stream has completed the slot's batch: copies the per-sample status words
  * (0 = ok, otherwise FFCVB_E_DECODE) into status[0..n).  Returns the number of failed samples.
