@@ -86,6 +86,7 @@ def parse_args():
     ap.add_argument('--no-cpu-baseline', action='store_true', help='skip the CPU oracle leg (profiling runs)')
     ap.add_argument('--no-configs', action='store_true', help='skip the short pass over the other configurations')
     ap.add_argument('--no-modes', action='store_true', help='skip the other staging modes (e2e_staged, e2e_gather, ...)')
+    ap.add_argument('--batch', type=int, default=0, help='profiling runs: batch size instead of the configuration\'s')
     ap.add_argument('--kernels-only', action='store_true',
                     help='profiling runs: stage the slots once, then only re-run the kernels on one stream')
     return ap.parse_args()
@@ -469,12 +470,12 @@ class Bench:
         return entry
 
     def link_peak(self, concurrent):
-        """Pinned 256 MB host->device copy, best of 5; `concurrent`: every rank copies at once."""
+        """Pinned 256 MB host->device copy, best of 10; `concurrent`: every rank copies at once."""
         ch = self.ch
         hbuf = ch.empty(256 << 20, dtype=ch.uint8).pin_memory()
         dbuf = ch.empty(256 << 20, dtype=ch.uint8, device=self.device)
         best = 1e9
-        for k in range(6):
+        for k in range(11):
             if concurrent:
                 self.barrier()
             a, b = ch.cuda.Event(enable_timing=True), ch.cuda.Event(enable_timing=True)
@@ -618,7 +619,7 @@ class Bench:
         out['path_bytes'] = mean['jpeg_bytes'] + crop_mean * raw_frac + out_bytes
         # units the ncu figures are scaled by
         out['units'] = {'entropy_decode': mean['scan_bytes'], 'idct': mean['blocks'],
-                        'upsample_colour': crop_mean * (1.0 - raw_frac) / 3.0,
+                        'upsample_colour': mean['n_jpeg'],
                         'resize_augment_normalise': float(batch * w['out'] * w['out'])}
         if loader._live_iterator is not None:
             loader._live_iterator.retire()
@@ -766,6 +767,8 @@ class Bench:
 
 if __name__ == '__main__':
     a = parse_args()
+    if a.batch:
+        WORKLOADS[a.config] = dict(WORKLOADS[a.config], batch=a.batch)
     if a.impl == 'reference':
         main_reference(a)
     else:

@@ -2,6 +2,8 @@
 // declared in include/ffcv_b200.h.
 #include <cuda_runtime.h>
 #include <emmintrin.h>
+#include <errno.h>
+#include <fcntl.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -227,6 +229,7 @@ struct ffcvb_ctx {
     std::mutex copy_m;
     std::condition_variable copy_cv;
     std::atomic<bool> copy_timeout{false};
+    std::atomic<bool> direct_broken{false}; // an O_DIRECT read was refused: buffered reads from now on
     Pool *pool = nullptr;
     std::string err;
     AuxBuf aux[16];
@@ -401,12 +404,53 @@ void ffcvb_destroy(ffcvb_ctx *ctx) {
 
 const char *ffcvb_last_error(const ffcvb_ctx *ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 
-int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const uint64_t *ptrs,
-                      const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
-                      const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params) {
+} // extern "C"
+
+namespace {
+
+// Where a batch's stored bytes come from: a mapping of the file (`base`), or file descriptors the
+// staging threads read from straight into the slot's pinned buffer (`fd` buffered, `fd_direct`
+// opened with O_DIRECT or -1).
+struct Source {
+    const uint8_t *base = nullptr;
+    int fd = -1, fd_direct = -1;
+    bool from_fd() const { return base == nullptr; }
+};
+
+// Reads [lo, lo + len) of the file into dst.  With O_DIRECT (offset, length and address are
+// multiples of 4096 then) the bytes never enter the page cache; a file system that refuses it at
+// read time is served through the buffered descriptor, whose pages are handed back afterwards so
+// that resident memory stays bounded by the slot ring.  Returns the bytes read (short at EOF).
+size_t read_range(const Source &src, std::atomic<bool> &direct_broken, uint8_t *dst, uint64_t lo, size_t len) {
+    size_t done = 0;
+    bool use_direct = src.fd_direct >= 0 && !direct_broken.load(std::memory_order_relaxed);
+    while (done < len) {
+        const ssize_t got = pread(use_direct ? src.fd_direct : src.fd, dst + done, len - done, (off_t)(lo + done));
+        if (got < 0) {
+            if (errno == EINTR) continue;
+            if (use_direct && errno == EINVAL) { // O_DIRECT not supported here after all
+                direct_broken.store(true, std::memory_order_relaxed);
+                use_direct = false;
+                continue;
+            }
+            break;
+        }
+        if (got == 0) break; // end of file
+        done += (size_t)got;
+        if (use_direct && (done & 4095)) break; // a short direct read only happens at the end of the file
+    }
+    if (!use_direct && done) posix_fadvise(src.fd, (off_t)lo, (off_t)done, POSIX_FADV_DONTNEED);
+    return done;
+}
+
+int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *ptrs,
+               const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
+               const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params) {
+    const uint8_t *file_base = source.base;
+    const bool from_fd = source.from_fd();
     if (!ctx) return FFCVB_E_ARG;
-    if (slot < 0 || slot >= (int)ctx->slots.size() || n <= 0 || !file_base || !ptrs || !sizes || !modes ||
-        !heights || !widths || !params)
+    if (slot < 0 || slot >= (int)ctx->slots.size() || n <= 0 || (!file_base && source.fd < 0) || !ptrs || !sizes ||
+        !modes || !heights || !widths || !params)
         return fail(ctx, FFCVB_E_ARG, "ffcvb_stage_batch: bad argument");
     if (!valid_plan(plan)) return fail(ctx, FFCVB_E_ARG, "ffcvb_stage_batch: invalid plan");
     CU(cudaSetDevice(ctx->device));
@@ -419,7 +463,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     // A source that lives in pinned (page-locked, device-mapped) host memory is not copied by the
     // CPU: the GPU gathers the payloads itself.
     uint64_t src_dev_base = 0;
-    {
+    if (!from_fd) {
         cudaPointerAttributes attr;
         memset(&attr, 0, sizeof(attr));
         if (cudaPointerGetAttributes(&attr, file_base) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
@@ -443,17 +487,76 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     s.src_ptrs.assign(ptrs, ptrs + n);
     s.headers.resize(n);
 
+    // ---- reading from file descriptors: every sample's bytes get their place in the pinned buffer
+    // before anything is parsed (a JPEG header can only be parsed once it has been read), so the
+    // parts of the blob whose size depends on the headers (tables, index lists) follow the payloads.
+    // With O_DIRECT a sample is read as the 4 KiB file blocks that contain it, into a 4 KiB aligned
+    // place: its first byte sits at the same offset inside a block as in the file.
+    struct Span {
+        uint64_t lo = 0;   // file offset the read starts at
+        size_t len = 0;    // bytes to read
+        size_t dst = 0;    // offset in the pinned buffer the read goes to
+        size_t skip = 0;   // the sample's first byte is dst + skip
+        uint64_t want = 0; // bytes of the sample needed from lo + skip on
+    };
+    std::vector<Span> spans;
+    const int n_params_early = 4 + 2 * plan->n_ops;
+    size_t fd_payload_begin = 0, fd_payload_end = 0;
+    if (from_fd) {
+        const size_t A = source.fd_direct >= 0 && !ctx->direct_broken.load() ? 4096 : kPayloadAlign;
+        size_t off = align_up(sizeof(BatchHeader), 16);
+        off = align_up(off + sizeof(ImageDesc) * (size_t)n, 16);
+        off = align_up(off + sizeof(int32_t) * (size_t)n * n_params_early, 16);
+        for (const auto &r : s.pending_riders) off = align_up(off, 64) + r.item_bytes * (uint64_t)n;
+        fd_payload_begin = off = align_up(off, A);
+        spans.resize(n);
+        for (int i = 0; i < n; i++) {
+            uint64_t start = ptrs[i], want = sizes[i];
+            if (modes[i] != FFCVB_MODE_JPG) {
+                int r0 = 0, rows = heights[i];
+                const int32_t *p = params + (size_t)i * n_params_early;
+                if (plan->resize && p[0] >= 0 && p[2] > 0 && p[0] + p[2] <= (int)heights[i] && p[1] >= 0 && p[3] > 0 &&
+                    p[1] + p[3] <= (int)widths[i]) {
+                    r0 = p[0];
+                    rows = p[2];
+                }
+                const uint64_t pitch = (uint64_t)widths[i] * 3;
+                if (sizes[i] < pitch * heights[i]) rows = 0; // short payload: flagged below, nothing read
+                start += (uint64_t)r0 * pitch;
+                want = (uint64_t)rows * pitch;
+            }
+            Span &sp = spans[i];
+            sp.want = want;
+            sp.lo = start / A * A;
+            sp.skip = (size_t)(start - sp.lo);
+            sp.len = want ? align_up(sp.skip + want, A) : 0;
+            sp.dst = off = align_up(off, A);
+            off += sp.len;
+        }
+        fd_payload_end = off;
+        // room behind the payloads for what is laid out after the parse: at most 255 tables of each kind
+        const size_t tail = 255 * (sizeof(HuffTable) + sizeof(MultTable)) + 3 * (sizeof(int32_t) * (size_t)n + 16) + 256;
+        int grc;
+        if ((grc = grow_host(ctx, s.host, s.host_cap, fd_payload_end + tail))) return grc;
+    }
+
     // ---- per-sample: parse headers, decide what to stage
-    ctx->pool->parallel_for(n, 8, [&](int i) {
+    ctx->pool->parallel_for(n, from_fd ? 1 : 8, [&](int i) {
         ImageDesc &d = descs[i];
         memset(&d, 0, sizeof(d));
         d.mode = modes[i];
         d.height = heights[i];
         d.width = widths[i];
-        const uint8_t *src = file_base + ptrs[i];
+        bool short_read = false;
+        if (from_fd && spans[i].len) {
+            const Span &sp = spans[i];
+            const size_t got = read_range(source, ctx->direct_broken, s.host + sp.dst, sp.lo, sp.len);
+            short_read = got < sp.skip + sp.want;
+        }
+        const uint8_t *src = from_fd ? s.host + spans[i].dst + spans[i].skip : file_base + ptrs[i];
         if (modes[i] == FFCVB_MODE_JPG) {
             JpegHeader &h = s.headers[i];
-            int rc = parse_jpeg_header(src, (size_t)sizes[i], &h);
+            int rc = short_read ? kErrData : parse_jpeg_header(src, (size_t)sizes[i], &h);
             if (rc == 0 && (h.width != d.width || h.height != d.height)) rc = kErrDims;
             d.host_status = (int16_t)rc;
             d.payload_size = (uint32_t)sizes[i];
@@ -504,9 +607,13 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                 }
             }
             const uint64_t need = (uint64_t)d.height * d.width * 3;
-            if (sizes[i] < need) {
+            if (sizes[i] < need || short_read) {
                 d.host_status = (int16_t)kErrData;
                 rows = 0;
+            }
+            if (from_fd) { // whole rows were read: the crop's columns are picked on the GPU
+                c0 = 0;
+                cols = d.width;
             }
             d.row0 = (uint16_t)r0;
             d.rows = (uint16_t)rows;
@@ -648,10 +755,21 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     size_t off = align_up(sizeof(BatchHeader), 16);
     hd.desc_off = off;
     off = align_up(off + sizeof(ImageDesc) * (size_t)n, 16);
-    hd.huff_off = off;
-    off = align_up(off + sizeof(HuffTable) * huff_src.size(), 16);
-    hd.mult_off = off;
-    off = align_up(off + sizeof(MultTable) * mult_src.size(), 16);
+    auto place_tables = [&] {
+        hd.huff_off = off;
+        off = align_up(off + sizeof(HuffTable) * huff_src.size(), 16);
+        hd.mult_off = off;
+        off = align_up(off + sizeof(MultTable) * mult_src.size(), 16);
+    };
+    auto place_lists = [&] {
+        s.jpeg_list_off = off;
+        off = align_up(off + sizeof(int32_t) * jpeg_list.size(), 16);
+        s.par_list_off = off;
+        off = align_up(off + sizeof(int32_t) * par_list.size(), 16);
+        s.seq_list_off = off;
+        off = align_up(off + sizeof(int32_t) * seq_list.size(), 16);
+    };
+    if (!from_fd) place_tables();
     hd.params_off = off;
     off = align_up(off + sizeof(int32_t) * (size_t)n * n_params, 16);
     s.riders.swap(s.pending_riders);
@@ -667,37 +785,43 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         off += r.bytes;
     }
     off = align_up(off, 16);
-    s.jpeg_list_off = off;
-    off = align_up(off + sizeof(int32_t) * jpeg_list.size(), 16);
-    s.par_list_off = off;
-    off = align_up(off + sizeof(int32_t) * par_list.size(), 16);
-    s.seq_list_off = off;
-    off = align_up(off + sizeof(int32_t) * seq_list.size(), 16);
-    hd.payload_off = off;
-    // payloads the staging threads copy come first: they travel with the head of the blob
-    for (int i = 0; i < n; i++) {
-        if (descs[i].src_addr != 0) continue;
-        descs[i].payload_off = off;
-        off = align_up(off + descs[i].payload_size, kPayloadAlign);
-    }
-    s.staged_end = off;
-    for (int i = 0; i < n; i++) {
-        ImageDesc &d = descs[i];
-        if (d.src_addr == 0) continue;
-        // Gathered payloads keep their source alignment mod 16 so that both sides move in whole
-        // 16-byte words.  A crop box is fetched row by row: every row gets a 16-byte aligned slot
-        // wide enough for the aligned words that contain it, and its pixels start inside the slot
-        // at the row's own source alignment (ImageDesc::raw_skew tells the reader).
-        const bool rowwise = d.mode == FFCVB_MODE_RAW && d.cols != d.width;
-        if (rowwise) {
-            d.raw_pitch = (uint32_t)align_up((size_t)d.cols * 3 + 15, 16);
-            d.payload_size = (uint32_t)((size_t)d.rows * d.raw_pitch);
-            d.raw_skew = 1;
-            d.payload_off = off;
-        } else {
-            d.payload_off = off + (d.src_addr & 15);
+    if (from_fd) {
+        // the payloads were read into their places before the parse; tables and lists follow them
+        if (off > fd_payload_begin) return fail(ctx, FFCVB_E_ARG, "ffcvb_stage_batch: the riders changed while the batch was staged");
+        hd.payload_off = fd_payload_begin;
+        for (int i = 0; i < n; i++) descs[i].payload_off = spans[i].dst + spans[i].skip;
+        off = align_up(fd_payload_end, 16);
+        place_tables();
+        place_lists();
+        s.staged_end = off;
+    } else {
+        place_lists();
+        hd.payload_off = off;
+        // payloads the staging threads copy come first: they travel with the head of the blob
+        for (int i = 0; i < n; i++) {
+            if (descs[i].src_addr != 0) continue;
+            descs[i].payload_off = off;
+            off = align_up(off + descs[i].payload_size, kPayloadAlign);
         }
-        off = align_up(d.payload_off + d.payload_size, kPayloadAlign);
+        s.staged_end = off;
+        for (int i = 0; i < n; i++) {
+            ImageDesc &d = descs[i];
+            if (d.src_addr == 0) continue;
+            // Gathered payloads keep their source alignment mod 16 so that both sides move in whole
+            // 16-byte words.  A crop box is fetched row by row: every row gets a 16-byte aligned slot
+            // wide enough for the aligned words that contain it, and its pixels start inside the slot
+            // at the row's own source alignment (ImageDesc::raw_skew tells the reader).
+            const bool rowwise = d.mode == FFCVB_MODE_RAW && d.cols != d.width;
+            if (rowwise) {
+                d.raw_pitch = (uint32_t)align_up((size_t)d.cols * 3 + 15, 16);
+                d.payload_size = (uint32_t)((size_t)d.rows * d.raw_pitch);
+                d.raw_skew = 1;
+                d.payload_off = off;
+            } else {
+                d.payload_off = off + (d.src_addr & 15);
+            }
+            off = align_up(d.payload_off + d.payload_size, kPayloadAlign);
+        }
     }
     hd.total_bytes = off;
 
@@ -723,8 +847,23 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
         if (!r.inline_bytes.empty()) {
             memcpy(s.host + r.off, r.inline_bytes.data(), r.bytes);
         } else {
-            for (int i = 0; i < n; i++)
-                memcpy(s.host + r.off + (size_t)i * r.item_bytes, file_base + r.ptrs[i], r.item_bytes);
+            for (int i = 0; i < n; i++) {
+                uint8_t *dst = s.host + r.off + (size_t)i * r.item_bytes;
+                if (!from_fd) {
+                    memcpy(dst, file_base + r.ptrs[i], r.item_bytes);
+                } else { // small items: buffered reads
+                    size_t done = 0;
+                    while (done < r.item_bytes) {
+                        const ssize_t got = pread(source.fd, dst + done, r.item_bytes - done, (off_t)(r.ptrs[i] + done));
+                        if (got < 0 && errno == EINTR) continue;
+                        if (got <= 0) {
+                            memset(dst + done, 0, r.item_bytes - done);
+                            break;
+                        }
+                        done += (size_t)got;
+                    }
+                }
+            }
         }
     }
     if (!jpeg_list.empty()) memcpy(s.host + s.jpeg_list_off, jpeg_list.data(), 4 * jpeg_list.size());
@@ -734,7 +873,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     const auto t2 = std::chrono::steady_clock::now();
     // ---- parallel: gather the payload bytes into pinned memory
     uint8_t *host = s.host;
-    if (s.staged_end > hd.payload_off) {
+    if (!from_fd && s.staged_end > hd.payload_off) {
         Slot *sp = &s; // the job may outlive this call: it only touches slot-owned data and the source
         ctx->pool->wait(Pool::kAsync); // one copy at a time: the batch staged before this one
         int copy_threads = direct ? ctx->split_copy_threads : 0;
@@ -775,7 +914,7 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
     s.stage_ms[0] = ms(t0, t1);
     s.stage_ms[1] = ms(t1, t2);
-    if (s.staged_end <= hd.payload_off) s.stage_ms[2] = 0; // else: written when the copy completes
+    if (from_fd || s.staged_end <= hd.payload_off) s.stage_ms[2] = 0; // else: written when the copy completes
     s.stage_ms[3] = ms(t0, t3);
     s.n_jpeg = (int)jpeg_list.size();
     s.n_par = (int)par_list.size();
@@ -808,6 +947,29 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
     }
     s.staged = true;
     return FFCVB_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const uint64_t *ptrs,
+                      const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
+                      const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params) {
+    if (ctx && !file_base) return fail(ctx, FFCVB_E_ARG, "ffcvb_stage_batch: bad argument");
+    Source src;
+    src.base = file_base;
+    return stage_impl(ctx, slot, src, ptrs, sizes, modes, heights, widths, n, plan, params);
+}
+
+int ffcvb_stage_batch_fd(ffcvb_ctx *ctx, int slot, int fd, int fd_direct, const uint64_t *ptrs,
+                         const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
+                         const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params) {
+    if (ctx && fd < 0) return fail(ctx, FFCVB_E_ARG, "ffcvb_stage_batch_fd: bad file descriptor");
+    Source src;
+    src.fd = fd;
+    src.fd_direct = fd_direct;
+    return stage_impl(ctx, slot, src, ptrs, sizes, modes, heights, widths, n, plan, params);
 }
 
 // Stream callback: holds the stream until the staging threads have finished the slot's payload
@@ -1005,7 +1167,9 @@ int64_t ffcvb_staged_bytes(const ffcvb_ctx *ctx, int slot) {
 }
 
 int ffcvb_stage_times(const ffcvb_ctx *ctx, int slot, double *ms) {
-    if (!ctx || !ms || slot < 0 || slot >= (int)ctx->slots.size() || !ctx->slots[slot].staged) return FFCVB_E_ARG;
+    // (no `staged` check: the figures of the slot's last completed staging stay readable while
+    // another thread stages the slot again)
+    if (!ctx || !ms || slot < 0 || slot >= (int)ctx->slots.size()) return FFCVB_E_ARG;
     for (int k = 0; k < 4; k++) ms[k] = ctx->slots[slot].stage_ms[k];
     return FFCVB_OK;
 }

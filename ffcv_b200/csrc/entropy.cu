@@ -58,6 +58,32 @@ __device__ __forceinline__ uint32_t peek32(const uint32_t *__restrict__ words, u
     return __funnelshift_l(words[i + 1], words[i], p);
 }
 
+// A 96-bit window over the stream kept in registers: hi holds the word the current position lies
+// in, lo the next one, nx the one after.  Looking at the next 32 bits is one funnel shift, and the
+// stream is touched once per 32 bits consumed (a predicated load, issued a symbol or more before
+// its value is needed) instead of twice per symbol, which takes the stream's load latency out of
+// the chain symbol -> table look-up -> next symbol.  Lanes never diverge: advancing is a select.
+struct BitWindow {
+    const uint32_t *__restrict__ w;
+    uint32_t wi, r, hi, lo, nx;
+    __device__ __forceinline__ BitWindow(const uint32_t *__restrict__ words, uint32_t p) : w(words), wi(p >> 5), r(p & 31) {
+        hi = w[wi];
+        lo = w[wi + 1];
+        nx = w[wi + 2];
+    }
+    __device__ __forceinline__ uint32_t peek() const { return __funnelshift_l(lo, hi, r); }
+    // consume n < 32 bits
+    __device__ __forceinline__ void skip(uint32_t n) {
+        r += n;
+        const bool adv = r >= 32;
+        hi = adv ? lo : hi;
+        lo = adv ? nx : lo;
+        wi += adv ? 1u : 0u;
+        r &= 31;
+        if (adv) nx = w[wi + 2];
+    }
+};
+
 // Entry (see HuffTable) of the Huffman code at the top of w: at most two dependent table reads.
 // An invalid code consumes 16 bits and acts as an end of block, so that speculative decoding
 // always makes progress.
@@ -122,8 +148,10 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
     int c = cur.c, z = cur.z;
     int comp2 = (ncomp == 1 || c < luma) ? 0 : 2 * (c - luma + 1);
     int16_t *out = cf + (size_t)blk * 64;
+    if (p >= end) return 0;
+    BitWindow win(words, p - bit_base);
     while (p < end) {
-        const uint32_t w = peek32(words, p - bit_base);
+        const uint32_t w = win.peek();
         const bool dc = z == 0;
         const HuffTable &t = s_tab[comp2 + (dc ? 0 : 1)];
         const uint32_t e = huff_lookup(t, w);
@@ -136,6 +164,7 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
                 out[dc ? 0 : s_zz[zpos]] = (int16_t)extend((w << (n - s)) >> (32 - s), s);
         }
         p += n;
+        win.skip(n);
         const bool eob = zn >= 64;
         z = eob ? 0 : zn;
         done += eob ? 1 : 0;
@@ -179,13 +208,15 @@ __device__ __forceinline__ int count_span_checked(const uint32_t *__restrict__ w
     uint32_t next_ck = start + (k + 1) * ck_bits;
     int total = -1;
     merged = false;
+    BitWindow win(words, p < end ? p : 0);
     while (p < end) {
-        const uint32_t w = peek32(words, p);
+        const uint32_t w = win.peek();
         const bool dc = z == 0;
         const HuffTable &t = s_tab[comp2 + (dc ? 0 : 1)];
         const uint32_t e = huff_lookup(t, w);
         const int zn = dc ? 1 : z + (int)(e >> 9);
         p += e & 31;
+        win.skip(e & 31);
         const bool eob = zn >= 64;
         z = eob ? 0 : zn;
         done += eob ? 1 : 0;
@@ -490,9 +521,10 @@ __device__ __forceinline__ uint32_t decode_interval(const uint32_t *__restrict__
     int c = 0, z = 0;
     int16_t *out = cf + (size_t)blk * 64;
     uint32_t done = 0;
+    BitWindow win(words, p);
     while (done < nblk) {
         if (p >= limit) return 0xFFFFFFFFu;
-        const uint32_t w = peek32(words, p);
+        const uint32_t w = win.peek();
         const bool dc = z == 0;
         const int comp = (ncomp == 1 || c < luma) ? 0 : c - luma + 1;
         const HuffTable &t = s_tab[2 * comp + (dc ? 0 : 1)];
@@ -508,6 +540,7 @@ __device__ __forceinline__ uint32_t decode_interval(const uint32_t *__restrict__
             out[s_zz[zpos]] = (int16_t)v;
         }
         p += n;
+        win.skip(n);
         if (zn >= 64) {
             z = 0;
             done++;

@@ -54,6 +54,9 @@ lib.ffcvb_last_error.restype = c_char_p
 lib.ffcvb_stage_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_int, POINTER(Plan), c_void_p]
 lib.ffcvb_stage_batch.restype = c_int
+lib.ffcvb_stage_batch_fd.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int, POINTER(Plan), c_void_p]
+lib.ffcvb_stage_batch_fd.restype = c_int
 lib.ffcvb_submit_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_submit_batch.restype = c_int
 lib.ffcvb_rerun_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
@@ -166,7 +169,8 @@ class Context:
             raise FFCVBError(f'{what} failed ({rc}): {msg.decode() if msg else ""}')
 
     def stage(self, slot, file_base, ptrs, sizes, modes, heights, widths, plan, params):
-        """file_base: integer address (or uint8 array) the sample pointers are relative to."""
+        """file_base: integer address (or uint8 array) the sample pointers are relative to, or a
+        (fd, fd_direct) pair of descriptors of the file to read the samples from."""
         ptrs = _as(ptrs, np.uint64)
         sizes = _as(sizes, np.uint64)
         modes = _as(modes, np.uint8)
@@ -175,6 +179,12 @@ class Context:
         params = _as(params, np.int32)
         n = len(ptrs)
         assert params.shape == (n, 4 + 2 * plan.n_ops), params.shape
+        if isinstance(file_base, tuple):
+            rc = lib.ffcvb_stage_batch_fd(self._h, slot, int(file_base[0]), int(file_base[1]), ptrs.ctypes.data,
+                                          sizes.ctypes.data, modes.ctypes.data, heights.ctypes.data,
+                                          widths.ctypes.data, n, ctypes.byref(plan), params.ctypes.data)
+            self._check(rc, 'ffcvb_stage_batch_fd')
+            return
         base = file_base.ctypes.data if isinstance(file_base, np.ndarray) else int(file_base)
         rc = lib.ffcvb_stage_batch(self._h, slot, base, ptrs.ctypes.data, sizes.ctypes.data,
                                    modes.ctypes.data, heights.ctypes.data, widths.ctypes.data, n,

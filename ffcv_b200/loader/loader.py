@@ -10,7 +10,7 @@ import torch as ch
 
 from .. import libffcv as L
 from ..fields.base import Field
-from ..memory_managers import MemoryManager, OSCacheManager, ReadAheadManager
+from ..memory_managers import DirectReadManager, MemoryManager, OSCacheManager
 from ..pipeline.compiler import Compiler
 from ..pipeline.graph import Graph
 from ..pipeline.operation import Operation
@@ -51,10 +51,11 @@ class Loader:
         count); < 1 means every core this process may run on.
     os_cache : bool
         The file is memory-mapped and served from the operating system's page cache.  ``False``
-        (the reference's process cache, for datasets larger than RAM) maps the file too, never
-        pins it, and lets the epoch's batch schedule drive the kernel's read-ahead: the byte
-        ranges of the next batches are requested ahead of time and those of finished batches are
-        handed back, so resident memory stays bounded.
+        (the reference's process cache, for datasets larger than RAM): the file is neither mapped
+        nor pinned; the staging threads read the samples of each batch (``pread``, with
+        ``O_DIRECT`` where the file system allows) straight into the pinned staging buffer of the
+        batch's slot, ``batches_ahead`` batches ahead of the consumer, so the bytes cross host
+        memory once and resident memory is bounded by the slot ring.
     order : OrderOption or TraversalOrder subclass
         SEQUENTIAL, RANDOM, QUASI_RANDOM, or a custom order.
     distributed : bool
@@ -164,12 +165,9 @@ class Loader:
                 self.memory_manager.open()
                 self.pin_file = self.memory_manager.pinned
         else:
-            # schedule-driven read-ahead over the mapping (the reference's process cache role)
-            md = self.reader.metadata
-            cols = [md[name]['data_ptr'] for name in md.dtype.names if 'data_ptr' in (md[name].dtype.names or ())]
-            ptrs = np.stack(cols, axis=1) if cols else np.zeros((self.reader.num_samples, 0), dtype=np.uint64)
-            self.memory_manager = ReadAheadManager(self.reader, ptrs, window=2 * (batches_ahead + 2),
-                                                   keep=batches_ahead + 3)
+            # no mapping, no page cache: the staging threads read every batch straight into the
+            # slot ring's pinned buffers (the reference's process cache role)
+            self.memory_manager = DirectReadManager(self.reader)
 
         if order in ORDER_MAP:
             self.traversal_order: TraversalOrder = ORDER_MAP[order](self)

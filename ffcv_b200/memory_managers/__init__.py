@@ -1,4 +1,4 @@
+from .direct_read import DirectReadManager, FileDescriptors
 from .os_cache import MemoryManager, OSCacheManager
-from .read_ahead import ReadAheadManager
 
-__all__ = ['MemoryManager', 'OSCacheManager', 'ReadAheadManager']
+__all__ = ['DirectReadManager', 'FileDescriptors', 'MemoryManager', 'OSCacheManager']

@@ -51,7 +51,8 @@ def standalone_decoder(op):
             plan.device = destination.device
             sample_sizes = sizes[np.searchsorted(ptrs, metadata['data_ptr'])]
             state['exe'] = FusedImageExecutor(plan, shared_context(destination.device), metadata, sample_sizes,
-                                              lambda: mmap.ctypes.data, np.random.randint(0, 2 ** 31 - 1))
+                                              (lambda: mmap) if isinstance(mmap, tuple) else (lambda: mmap.ctypes.data),
+                                              np.random.randint(0, 2 ** 31 - 1))
             state['calls'] = 0
         state['calls'] += 1
         stream = ch.cuda.current_stream(destination.device)

@@ -106,6 +106,21 @@ int ffcvb_stage_batch(ffcvb_ctx *ctx, int slot, const uint8_t *file_base, const 
                       const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
                       const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params);
 
+/* ffcvb_stage_batch for a file that is not mapped (datasets larger than RAM; the role of
+ * ffcv/memory_managers/process_cache/page_reader.py:9-40, whose reader threads load 8 MiB pages
+ * into a page ring the decoders then copy from).  Here the staging threads `pread` every sample
+ * straight into its place in the slot's pinned buffer -- the only host buffer the bytes ever
+ * touch -- and parse the JPEG headers there.  `fd`: the file opened for reading; `fd_direct`: the
+ * same file opened with O_DIRECT, or -1.  With O_DIRECT a sample travels as the 4 KiB blocks that
+ * contain it (read into a 4 KiB aligned place, so at most 8 KiB more per sample cross the link) and
+ * never enters the page cache; when the file system refuses O_DIRECT, reads go through `fd` and the
+ * pages they brought in are handed back right away (posix_fadvise DONTNEED).  Raw samples are read
+ * as the whole rows their crop box touches.  The call returns when everything has been read:
+ * ffcvb_stage_times()[0] is then read + parse time.  Everything else as ffcvb_stage_batch. */
+int ffcvb_stage_batch_fd(ffcvb_ctx *ctx, int slot, int fd, int fd_direct, const uint64_t *ptrs,
+                         const uint64_t *sizes, const uint8_t *modes, const uint16_t *heights,
+                         const uint16_t *widths, int n, const ffcvb_plan *plan, const int32_t *params);
+
 /* Riders: values of the samples' other fields that travel inside the image batch's staged bytes, so
  * that a whole batch (pixels, labels, small arrays) is one host->device transfer.  Replaces the
  * separate per-batch copy that IntDecoder / FloatDecoder / NDArrayDecoder followed by ToTensor and

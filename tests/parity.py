@@ -27,8 +27,7 @@ def image_executor(loader, field='image'):
 def oracle_batch(loader, executor, batch_indices, params, nthreads=4):
     """Expected output of one fused batch, as a numpy array laid out like the device buffer."""
     plan = executor.plan
-    mm = loader.memory_manager
-    mmap = mm.open()
+    mmap = np.memmap(loader.reader.file_name, dtype=np.uint8, mode='r')  # whatever the loader's own access is
     md = executor.metadata[batch_indices]
     sizes = executor.sample_sizes[batch_indices]
     payloads = [np.array(mmap[int(p):int(p) + int(s)]) for p, s in zip(md['data_ptr'], sizes)]

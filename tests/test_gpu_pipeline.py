@@ -384,3 +384,59 @@ def test_fixed_size_jpeg_labels_arrays_and_two_image_fields(tmp_path):
     # pixels of both image fields against the oracle (fresh loaders: every epoch redraws)
     assert compare_epoch(_loader(path, 32, pipes), field_pos=0, field='image') == n * h * w * 3
     assert compare_epoch(_loader(path, 32, pipes), field_pos=4, field='mask') == n * 40 * 40 * 3
+
+
+def _resident_fraction(path):
+    """Share of the file's pages that the page cache holds (mincore over a mapping)."""
+    import ctypes
+    import mmap
+    size = os.path.getsize(path)
+    with open(path, 'rb') as fp:
+        mm = mmap.mmap(fp.fileno(), 0, prot=mmap.PROT_READ)
+    pages = (size + mmap.PAGESIZE - 1) // mmap.PAGESIZE
+    vec = (ctypes.c_ubyte * pages)()
+    libc = ctypes.CDLL(None, use_errno=True)
+    arr = np.frombuffer(mm, dtype=np.uint8)
+    rc = libc.mincore(ctypes.c_void_p(arr.ctypes.data), ctypes.c_size_t(size), vec)
+    frac = sum(v & 1 for v in vec) / pages if rc == 0 else None
+    del arr
+    mm.close()
+    return frac
+
+
+@pytest.mark.parametrize('direct_io', [True, False], ids=['o_direct', 'buffered'])
+def test_larger_than_ram_path_reads_straight_into_pinned_buffers(tmp_path, direct_io):
+    """Loader(os_cache=False): nothing is mapped, the staging threads pread every batch into the
+    slot's pinned buffer (O_DIRECT where the file system takes it, else buffered reads whose pages
+    are dropped again).  Same pixels and labels; the page cache does not fill up with the file."""
+    from ffcv_b200 import OrderOption
+    from ffcv_b200.fields.decoders import IntDecoder, RandomResizedCropRGBImageDecoder
+    from ffcv_b200.memory_managers import DirectReadManager
+    from ffcv_b200.synthetic import write_dataset_isolated as write_dataset
+    from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, Squeeze, ToDevice, ToTensor, ToTorchImage
+    path = write_dataset(2, str(tmp_path / 'c2_direct.beton'), 160, num_workers=8)
+    dev = ch.device('cuda:0')
+    pipes = {'image': [RandomResizedCropRGBImageDecoder((224, 224)), RandomHorizontalFlip(),
+                       NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()],
+             'label': [IntDecoder(), ToTensor(), ToDevice(dev), Squeeze()]}
+    os.sync()  # freshly written pages are dirty, and dirty pages cannot be dropped
+    fd = os.open(path, os.O_RDONLY)
+    os.posix_fadvise(fd, 0, 0, os.POSIX_FADV_DONTNEED)
+    os.close(fd)
+    before = _resident_fraction(path)
+    loader = _loader(path, 32, pipes, order=OrderOption.QUASI_RANDOM, os_cache=False)
+    assert isinstance(loader.memory_manager, DirectReadManager)
+    loader.memory_manager.direct_io = direct_io
+    labels = []
+    exe = image_executor(loader)
+    exe.param_log = []
+    for b in loader:
+        labels.append(b[1].clone())
+    order = np.concatenate([ix for (_, _, ix, _) in exe.param_log])
+    exe.param_log = None
+    assert np.array_equal(ch.cat(labels).cpu().numpy(), loader.reader.metadata['f1'][order])
+    after = _resident_fraction(path)
+    compare_epoch(loader)
+    # On a file system that can drop clean pages (not tmpfs) an epoch leaves the cache as it found it.
+    if before is not None and after is not None and before < 0.5:
+        assert after < before + 0.15, (before, after)

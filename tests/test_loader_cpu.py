@@ -157,38 +157,28 @@ def test_invalid_arguments(beton):
         Loader(beton, batch_size=8, pipelines={'image': None}, cpu_stage_share=1.5)
 
 
-def test_read_ahead_manager_follows_the_schedule(beton):
-    """os_cache=False: the byte ranges of upcoming batches are requested ahead of the pipeline and
-    released behind it (a recording stand-in replaces posix_fadvise); results are unchanged."""
-    import os
-    from ffcv_b200.memory_managers import ReadAheadManager
-    from ffcv_b200.memory_managers.read_ahead import merge_ranges
-    assert merge_ranges([10000, 100, 5000000], [50, 5000, 10]) == [(0, 12288), (4997120, 4096)]
+def test_direct_read_manager_reads_without_a_mapping(beton):
+    """os_cache=False: the file is not mapped; `memory_read` serves payloads with pread, the
+    label path is unchanged, and the native staging call gets the file descriptors."""
+    from ffcv_b200.memory_managers import DirectReadManager, FileDescriptors, OSCacheManager
+    from ffcv_b200.reader import Reader
     truth = _labels(beton)
     loader = _loader(beton, batch_size=32, drop_last=False, os_cache=False)
     mm = loader.memory_manager
-    assert isinstance(mm, ReadAheadManager) and not loader.pin_file
-    calls = []
-    mm.advise = lambda fd, start, length, flag: calls.append((start, length, flag))
+    assert isinstance(mm, DirectReadManager) and not loader.pin_file and mm.direct
     got = ch.cat([b[0].clone() for b in loader]).numpy().ravel()
     assert np.array_equal(got, truth)
-    loader._live_iterator.retire() if loader._live_iterator is not None else None
-    want = [c for c in calls if c[2] == os.POSIX_FADV_WILLNEED]
-    drop = [c for c in calls if c[2] == os.POSIX_FADV_DONTNEED]
-    assert want and drop
-    # every sample's payload lies inside a requested range
-    ptrs = loader.reader.metadata['f0']['data_ptr']
-    sizes = mm.sizes_of(ptrs)
-    covered = np.zeros(len(ptrs), bool)
-    for start, length, _ in want:
-        covered |= (ptrs >= start) & (ptrs + sizes <= start + length)
-    assert covered.all()
-    # nothing is released before it was requested
-    first_want = {}
-    for k, c in enumerate(calls):
-        if c[2] == os.POSIX_FADV_WILLNEED:
-            first_want.setdefault(c[:2], k)
-    assert all(first_want.get(c[:2], -1) < k for k, c in enumerate(calls) if c[2] == os.POSIX_FADV_DONTNEED)
+    fds = mm.file_base()
+    assert isinstance(fds, FileDescriptors) and fds.fd >= 0
+    # payload bytes read through the descriptor equal those of the mapping
+    r = Reader(beton)
+    mapped = OSCacheManager(r)
+    read_fd, read_map = mm.compile_reader(), mapped.compile_reader()
+    state_fd, state_map = mm.schedule_epoch([]).state, mapped.schedule_epoch([]).__enter__().state
+    for ptr in r.metadata['f0']['data_ptr'][[0, 7, 202]]:
+        assert np.array_equal(read_fd(ptr, state_fd), np.asarray(read_map(ptr, state_map)))
+    mm.close()
+    assert mm.fds is None
 
 
 def test_ndarray_field_round_trip(tmp_path):
