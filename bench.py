@@ -522,7 +522,9 @@ class Bench:
                 res = self.run_e2e(probe, steps, warmup)
                 others[name] = self.e2e_entry(res, source=self.describe(probe))
                 del probe
+        t_setup = time.perf_counter()
         loader = self.make_loader(cfg, path)
+        setup_s = time.perf_counter() - t_setup  # includes page-locking the file where it lies
         exe = loader.graph.pipelines[0].executor
         ctx = exe.ctx
         slots = loader.batches_ahead + 2
@@ -530,6 +532,8 @@ class Bench:
         if not args.kernels_only:
             res = self.run_e2e(loader, steps, warmup, sampler)
             out['e2e'] = self.e2e_entry(res, source=self.describe(loader))
+            out['e2e']['loader_setup_s'] = setup_s
+            out['e2e']['file_bytes'] = os.path.getsize(path)
             out['e2e_raw'] = res
             out.update(others)
             out['launches_per_batch'] = res['launches']

@@ -2,7 +2,6 @@
 iteration protocol; batches are decoded and augmented on the GPU of the calling process."""
 import enum
 from os import environ, sched_getaffinity
-from os.path import getsize
 from typing import Any, Callable, Mapping, Sequence, Type, Union
 
 import numpy as np
@@ -81,10 +80,11 @@ class Loader:
         bytes cross host memory once instead of three times.  A file on a memory file system
         (``/dev/shm``) is page-locked where it lies, so all processes of a node share the one
         copy and nothing is read at start-up; any other file costs one pinned copy per process.
-        Default (``None``): a file of at most ``FFCV_B200_PIN_LIMIT_GB`` (default 64) GiB is
-        page-locked in place when it lies on a memory file system, and otherwise copied only if
-        the copies of all ranks of the host (``LOCAL_WORLD_SIZE``) fit half of the memory
-        available now; else the staged path is used.  Measured on config 2: 1 GPU + 16 threads
+        Default (``None``): a file on a memory file system is page-locked where it lies, whatever
+        its size (nothing is copied); any other file is copied into pinned memory only if it is at
+        most ``FFCV_B200_PIN_LIMIT_GB`` (default 64) GiB and the copies of all ranks of the host
+        (``LOCAL_WORLD_SIZE``) fit half of the memory available now; else the staged path is used.
+        Measured on config 2: 1 GPU + 16 threads
         255-270 k img/s staged, 250-270 k gathered, 300-330 k split (below); 8 GPUs + 32 cores
         326 k staged, 1.15 M gathered.  ``FFCV_B200_PIN_FILE`` = 0 / 1 overrides.
     cpu_stage_share : float
@@ -145,8 +145,9 @@ class Loader:
         if not os_cache:
             pin_file = False  # the file is taken to be larger than RAM
         if pin_file is None:
-            limit = float(environ.get('FFCV_B200_PIN_LIMIT_GB', '64')) * (1 << 30)
-            pin_file = 'auto' if ch.cuda.is_available() and getsize(fname) <= limit else False
+            # 'auto': page-lock the file where it lies if it is on a memory file system (no copy,
+            # whatever its size); a private pinned copy only below the limit and if it fits
+            pin_file = 'auto' if ch.cuda.is_available() else False
         self.pin_file = bool(pin_file)
         if cpu_stage_share is None and 'FFCV_B200_STAGE_SPLIT' in environ:
             cpu_stage_share = int(environ['FFCV_B200_STAGE_SPLIT']) / 1000

@@ -88,7 +88,10 @@ class OSCacheManager(MemoryManager):
     def _private_copy_fits(self):
         import os
         ranks = max(1, int(os.environ.get('LOCAL_WORLD_SIZE', '1')))
-        need = os.path.getsize(self.reader.file_name) * ranks
+        size = os.path.getsize(self.reader.file_name)
+        if size > float(os.environ.get('FFCV_B200_PIN_LIMIT_GB', '64')) * (1 << 30):
+            return False
+        need = size * ranks
         try:
             with open('/proc/meminfo') as fp:
                 avail = next(int(ln.split()[1]) * 1024 for ln in fp if ln.startswith('MemAvailable:'))

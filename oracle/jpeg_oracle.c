@@ -463,6 +463,65 @@ static void idct_accurate_block(const int16_t *coef, const uint16_t *quant, uint
     }
 }
 
+/* ------------------------------------------------------------ reduced-size inverse transforms
+ * Decoding at 1/2, 1/4 or 1/8 scale (libjpeg's scale_num / scale_denom, the arguments
+ * libffcv/libffcv.cpp:59,89-90 passes to TurboJPEG) inverts every block straight to 4x4, 2x2 or
+ * 1x1 samples.  Mathematically an output sample is the mean of the r x r samples (r = 2, 4, 8)
+ * of the full inverse transform that it replaces.  Per dimension, with the 8-point transform in
+ * the scaling the integer transforms use, x[n] = a0 + sqrt(2) sum_k a_k cos((2n+1) k pi / 16), the
+ * sum of r neighbours is
+ *     S[m] = r a0 + sum_k a_k C_r(k, m),   C_r(k, m) = sqrt(2) sum_{j<r} cos((2 (r m + j) + 1) k pi / 16)
+ * (C vanishes for k = 4 when r = 2 and for every even k when r >= 4).  libjpeg-turbo evaluates
+ * exactly this with 13-bit constants round(|C| 2^13), 32-bit sums, dequantisation by the plain
+ * quantiser step, two extra fraction bits after the column pass, and one rounding shift per pass
+ * that also divides by r; the result is pinned against its binary in the tests. */
+#include <math.h>
+
+static void reduced_constants(int r, int32_t c[8][4]) {
+    const double pi = 3.14159265358979323846;
+    for (int k = 0; k < 8; k++)
+        for (int m = 0; m < 8 / r; m++) {
+            double v = 0;
+            for (int j = 0; j < r; j++) v += cos((2 * (r * m + j) + 1) * k * pi / 16.0);
+            v *= sqrt(2.0);
+            double a = fabs(v);
+            int32_t q = a < 1e-9 ? 0 : (int32_t)(a * 8192.0 + 0.5);
+            c[k][m] = v < 0 ? -q : q;
+        }
+}
+
+/* in[8] (in[k] for the k the size uses) -> out[8 / r], rounding shift `shift`. */
+static void reduced_1d(const int32_t in[8], int32_t *out, int r, int log2r, const int32_t c[8][4], int shift) {
+    for (int m = 0; m < 8 / r; m++) {
+        int32_t acc = in[0] * (1 << (13 + log2r));
+        for (int k = 1; k < 8; k++) acc += in[k] * c[k][m];
+        out[m] = (acc + (1 << (shift - 1))) >> shift;
+    }
+}
+
+/* coef: 64 quantised coefficients, natural order; writes (8 / r)^2 samples. */
+static void idct_reduced_block(const int16_t *coef, const uint16_t *quant, uint8_t *out, int stride, int r) {
+    const int log2r = r == 2 ? 1 : (r == 4 ? 2 : 3), n = 8 / r;
+    int32_t c[8][4];
+    reduced_constants(r, c);
+    int32_t ws[8][4]; /* [column of the block][row of the result] */
+    for (int col = 0; col < 8; col++) {
+        int32_t in[8], res[4];
+        for (int k = 0; k < 8; k++) in[k] = (int32_t)coef[k * 8 + col] * quant[k * 8 + col];
+        reduced_1d(in, res, r, log2r, c, 13 - 2 + log2r);
+        for (int m = 0; m < n; m++) ws[col][m] = res[m];
+    }
+    for (int row = 0; row < n; row++) {
+        int32_t in[8], res[4];
+        for (int k = 0; k < 8; k++) in[k] = ws[k][row];
+        reduced_1d(in, res, r, log2r, c, 13 + 2 + 3 + log2r);
+        for (int m = 0; m < n; m++) {
+            int v = res[m] + 128;
+            out[row * stride + m] = (uint8_t)(v < 0 ? 0 : (v > 255 ? 255 : v));
+        }
+    }
+}
+
 static void fast_multipliers(const uint16_t *quant, int16_t *mult) {
     int32_t s[64];
     aan_scale14(s);
@@ -614,9 +673,73 @@ int oracle_jpeg_decode(const uint8_t *data, size_t n, uint8_t *out, int height, 
     return ORACLE_OK;
 }
 
-/* Same signature as libffcv/libffcv.cpp:53-61 `imdecode`; the crop/flip/scale arguments are
- * accepted and, as in every call the reference makes (fields/rgb_image.py:131-132,196-197),
- * must be the identity. */
+/* Which scale a stream can be decoded at: three components, no chroma subsampling or 2x2. */
+int oracle_jpeg_scalable(const uint8_t *data, size_t n) {
+    Jpeg j;
+    if (parse_headers(data, n, &j)) return 0;
+    return j.ncomp == 3 && ((j.hmax == 1 && j.vmax == 1) || (j.hmax == 2 && j.vmax == 2));
+}
+
+/* Decode at 1 / denom (denom = 2, 4, 8) to packed RGB of ceil(height / denom) x ceil(width / denom)
+ * pixels, the way libjpeg-turbo does with scale_num / scale_denom = 1 / denom, the fast integer
+ * transform selected and fancy upsampling on: the luma blocks are inverted at 8 / denom samples a
+ * side; with 2x2 chroma subsampling the chroma blocks are inverted at twice that (at most 8: the
+ * full-size fast transform), which brings them to the luma resolution, so that no upsampling
+ * step is left.  out_h / out_w must be those dimensions. */
+int oracle_jpeg_decode_scaled(const uint8_t *data, size_t n, uint8_t *out, int out_h, int out_w, int denom) {
+    Jpeg j;
+    int rc = parse_headers(data, n, &j);
+    if (rc) return rc;
+    if (denom != 2 && denom != 4 && denom != 8) return ORACLE_ERR_UNSUPPORTED;
+    if (j.ncomp != 3 || !((j.hmax == 1 && j.vmax == 1) || (j.hmax == 2 && j.vmax == 2))) return ORACLE_ERR_UNSUPPORTED;
+    if (out_w != (j.width + denom - 1) / denom || out_h != (j.height + denom - 1) / denom) return ORACLE_ERR_DIMS;
+    size_t nblocks = total_blocks(&j);
+    int16_t *coef = (int16_t *)malloc(nblocks * 64 * sizeof(int16_t));
+    if (!coef) return ORACLE_ERR_DATA;
+    rc = decode_scan(&j, coef, nblocks);
+    if (rc) {
+        free(coef);
+        return rc;
+    }
+    int16_t mult[3][64];
+    int bs[3]; /* samples a side a block of each component is inverted to */
+    for (int c = 0; c < 3; c++) {
+        Component *k = &j.comp[c];
+        bs[c] = 8 / denom * (j.hmax / k->hs);
+        if (bs[c] > 8) bs[c] = 8;
+        k->plane_w = k->blocks_w * bs[c];
+        k->plane_h = k->blocks_h * bs[c];
+        k->plane = (uint8_t *)malloc((size_t)k->plane_w * k->plane_h);
+        fast_multipliers(j.quant[k->tq], mult[c]);
+    }
+    size_t blk = 0;
+    for (int my = 0; my < j.mcus_y; my++)
+        for (int mx = 0; mx < j.mcus_x; mx++)
+            for (int c = 0; c < 3; c++) {
+                Component *k = &j.comp[c];
+                for (int v = 0; v < k->vs; v++)
+                    for (int h = 0; h < k->hs; h++, blk++) {
+                        uint8_t *dst = k->plane + (size_t)((my * k->vs + v) * bs[c]) * k->plane_w +
+                                       (mx * k->hs + h) * bs[c];
+                        if (bs[c] == 8)
+                            idct_fast_block(coef + blk * 64, mult[c], dst, k->plane_w);
+                        else
+                            idct_reduced_block(coef + blk * 64, j.quant[k->tq], dst, k->plane_w, 8 / bs[c]);
+                    }
+            }
+    for (int y = 0; y < out_h; y++)
+        for (int x = 0; x < out_w; x++)
+            ycc_to_rgb(j.comp[0].plane[(size_t)y * j.comp[0].plane_w + x], j.comp[1].plane[(size_t)y * j.comp[1].plane_w + x],
+                       j.comp[2].plane[(size_t)y * j.comp[2].plane_w + x], out + ((size_t)y * out_w + x) * 3);
+    for (int c = 0; c < 3; c++) free(j.comp[c].plane);
+    free(coef);
+    return ORACLE_OK;
+}
+
+/* Same signature as libffcv/libffcv.cpp:53-61 `imdecode`.  The crop and flip arguments must be
+ * the identity, as in every call the reference makes (fields/rgb_image.py:131-132,196-197); the
+ * scale may be 1/1 (what the reference passes) or 1/2, 1/4, 1/8, in which case crop_height /
+ * crop_width are the scaled dimensions, as TurboJPEG expects them. */
 int imdecode(unsigned char *input_buffer, uint64_t input_size, uint32_t source_height,
              uint32_t source_width, unsigned char *output_buffer, uint32_t crop_height,
              uint32_t crop_width, uint32_t offset_x, uint32_t offset_y, uint32_t scale_num,
@@ -625,9 +748,15 @@ int imdecode(unsigned char *input_buffer, uint64_t input_size, uint32_t source_h
     (void)source_width;
     (void)offset_x;
     (void)offset_y;
-    if (enable_crop || hflip || scale_num != scale_denom) return -1;
-    int rc = oracle_jpeg_decode(input_buffer, (size_t)input_size, output_buffer, (int)crop_height,
+    if (enable_crop || hflip || scale_num == 0 || scale_denom % scale_num != 0) return -1;
+    const uint32_t denom = scale_denom / scale_num;
+    int rc;
+    if (denom == 1)
+        rc = oracle_jpeg_decode(input_buffer, (size_t)input_size, output_buffer, (int)crop_height,
                                 (int)crop_width, IDCT_FAST, UPSAMPLE_FANCY);
+    else
+        rc = oracle_jpeg_decode_scaled(input_buffer, (size_t)input_size, output_buffer, (int)crop_height,
+                                       (int)crop_width, (int)denom);
     return rc ? -1 : 0;
 }
 

@@ -41,6 +41,8 @@ def lib():
         L.oracle_jpeg_num_blocks.restype = ctypes.c_int64
         L.oracle_jpeg_coefficients.argtypes = [vp, sz, vp]
         L.oracle_jpeg_decode.argtypes = [vp, sz, vp, ci, ci, ci, ci]
+        L.oracle_jpeg_decode_scaled.argtypes = [vp, sz, vp, ci, ci, ci]
+        L.oracle_jpeg_scalable.argtypes = [vp, sz]
         L.oracle_resize_area.argtypes = [vp, ci, ci, ci, ci, ci, vp, ci, ci]
         L.oracle_resize_area.restype = None
         L.oracle_augment.argtypes = [vp, ci, ci, vp, ci, vp]
@@ -79,6 +81,24 @@ def jpeg_decode(buf, idct=IDCT_FAST, upsample=UPSAMPLE_FANCY):
     if rc:
         raise ValueError(f'oracle_jpeg_decode: {rc}')
     return out
+
+
+def jpeg_decode_scaled(buf, denom):
+    """Decode at 1 / denom (2, 4 or 8) to (ceil(h / denom), ceil(w / denom), 3) uint8 RGB, as
+    libjpeg-turbo does with scale 1 / denom, the fast integer transform and fancy upsampling."""
+    buf = np.ascontiguousarray(buf, dtype=np.uint8)
+    info = jpeg_info(buf)
+    h, w = -(-info['height'] // denom), -(-info['width'] // denom)
+    out = np.empty((h, w, 3), dtype=np.uint8)
+    rc = lib().oracle_jpeg_decode_scaled(buf.ctypes.data, buf.size, out.ctypes.data, h, w, int(denom))
+    if rc:
+        raise ValueError(f'oracle_jpeg_decode_scaled: {rc}')
+    return out
+
+
+def jpeg_scalable(buf):
+    buf = np.ascontiguousarray(buf, dtype=np.uint8)
+    return bool(lib().oracle_jpeg_scalable(buf.ctypes.data, buf.size))
 
 
 def jpeg_coefficients(buf):

@@ -10,6 +10,8 @@ jpeg_cases.npz    JPEG streams written by cv2.imencode (the call the reference's
                   `fast_replicate_*` = Pillow with decoder config (scale 1, draft 1) = fast integer
                   IDCT + replicated chroma; `accurate_fancy_*` = cv2.imdecode = accurate IDCT +
                   triangle ("fancy") upsampling.
+jpeg_scaled_cases.npz the same streams decoded at 1/2, 1/4 and 1/8 scale by that library with the
+                  fast integer IDCT selected (what TurboJPEG does with a scaling factor).
 resize_cases.npz  inputs and outputs of cv2.resize(INTER_AREA), the call of libffcv.cpp:40-41.
 crop_cases.npz    crop boxes from the reference's own get_random_crop / get_center_crop
                   (function source taken from ffcv/fields/rgb_image.py of the checkout at
@@ -93,6 +95,21 @@ def jpeg_cases():
         out[f'turbo_fast_fancy_{k}'] = libjpeg_direct.decode(buf, libjpeg_direct.JDCT_IFAST, True)
     out['count'] = np.array(len(specs))
     np.savez_compressed(os.path.join(HERE, 'jpeg_cases.npz'), **out)
+
+
+def jpeg_scaled_cases():
+    """The streams of jpeg_cases.npz decoded at 1/2, 1/4 and 1/8 by Pillow's libjpeg-turbo through the
+    libjpeg API (scale_num / scale_denom, fast integer IDCT selected, fancy upsampling on)."""
+    z = np.load(os.path.join(HERE, 'jpeg_cases.npz'))
+    out = {}
+    kept = 0
+    for k in range(int(z['count'])):
+        buf = z[f'jpeg_{k}']
+        for denom in (2, 4, 8):
+            out[f'scaled_{k}_{denom}'] = libjpeg_direct.decode(buf, libjpeg_direct.JDCT_IFAST, True, denom)
+        kept += 1
+    out['count'] = np.array(kept)
+    np.savez_compressed(os.path.join(HERE, 'jpeg_scaled_cases.npz'), **out)
 
 
 def resize_cases():
@@ -263,14 +280,20 @@ def pixel_cases():
 if __name__ == '__main__':
     import argparse
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', required=True, help='root of the libffcv/ffcv checkout')
-    ap.add_argument('what', nargs='?', default='all', choices=['all', 'pixel'])
+    ap.add_argument('--reference', help='root of the libffcv/ffcv checkout (not needed for `scaled`)')
+    ap.add_argument('what', nargs='?', default='all', choices=['all', 'pixel', 'scaled'])
     cli = ap.parse_args()
+    if cli.what == 'scaled':
+        jpeg_scaled_cases()
+        raise SystemExit
+    if not cli.reference:
+        ap.error('--reference is required')
     REF_ROOT = os.path.abspath(cli.reference)
     if cli.what == 'pixel':
         pixel_cases()
         raise SystemExit
     jpeg_cases()
+    jpeg_scaled_cases()
     resize_cases()
     crop_cases()
     normalize_cases()

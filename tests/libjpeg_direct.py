@@ -71,8 +71,10 @@ def available():
     return library_path() is not None and struct_size() is not None
 
 
-def decode(buf, dct_method=JDCT_IFAST, fancy_upsampling=True):
-    """RGB pixels of a 3-component JPEG stream as this libjpeg-turbo decodes them."""
+def decode(buf, dct_method=JDCT_IFAST, fancy_upsampling=True, scale_denom=1):
+    """RGB pixels of a 3-component JPEG stream as this libjpeg-turbo decodes them; with
+    `scale_denom` > 1 at scale 1 / scale_denom (scale_num at byte 68, scale_denom at byte 72 of the
+    struct, both 1 by default; output_width / output_height at bytes 136 / 140)."""
     lib = _lib()
     buf = np.ascontiguousarray(buf, dtype=np.uint8)
     cinfo = ctypes.create_string_buffer(4096)
@@ -88,7 +90,15 @@ def decode(buf, dct_method=JDCT_IFAST, fancy_upsampling=True):
         raise RuntimeError('unexpected jpeg_decompress_struct layout')
     ints[24] = int(dct_method)
     ints[25] = 1 if fancy_upsampling else 0
+    if scale_denom != 1:
+        if ints[17] != 1 or ints[18] != 1:
+            raise RuntimeError('unexpected jpeg_decompress_struct layout (scale)')
+        ints[18] = int(scale_denom)
     lib.jpeg_start_decompress(cinfo)
+    if scale_denom != 1:
+        if ints[34] != -(-w // scale_denom) or ints[35] != -(-h // scale_denom):
+            raise RuntimeError('unexpected jpeg_decompress_struct layout (output size)')
+        w, h = ints[34], ints[35]
     out = np.zeros((h, w, 3), dtype=np.uint8)
     row = 0
     while row < h:

@@ -61,3 +61,19 @@ def test_normalize_tables_against_reference_expression():
             assert np.array_equal(op.lookup_table.view(np.uint16 if dt == np.float16 else np.uint32),
                                   want.view(np.uint16 if dt == np.float16 else np.uint32))
             assert np.array_equal(O.normalize_table(z[f'{name}_mean'], z[f'{name}_std'], dt), want)
+
+
+def test_scaled_decode_against_libjpeg_turbo_vectors():
+    """Decoding at 1/2, 1/4 and 1/8 (reduced-size inverse transforms; chroma of 4:2:0 streams at
+    twice the luma's block size, hence no upsampling)."""
+    z = np.load(os.path.join(G, 'jpeg_cases.npz'))
+    s = np.load(os.path.join(G, 'jpeg_scaled_cases.npz'))
+    checked = 0
+    for k in range(int(z['count'])):
+        buf = z[f'jpeg_{k}']
+        if not O.jpeg_scalable(buf):
+            continue  # 4:2:2: scaling is not offered for it
+        for denom in (2, 4, 8):
+            assert np.array_equal(O.jpeg_decode_scaled(buf, denom), s[f'scaled_{k}_{denom}']), (k, denom)
+            checked += 1
+    assert checked >= 30

@@ -162,3 +162,20 @@ def test_augment_and_normalize_follow_numpy_semantics():
                           O.OUT_F16_NCHW)
     want = table[img, np.arange(3)[None, None, :]].transpose(2, 0, 1)
     assert st[0] == 0 and np.array_equal(out[0].view(np.uint16), want.view(np.uint16))
+
+
+def test_scaled_decode_against_libjpeg_turbo_directly():
+    """Scales 1/2, 1/4, 1/8 with the fast integer IDCT selected, decoded by the libjpeg-turbo binary
+    bundled with Pillow: random sizes and contents, 4:2:0 and 4:4:4, several qualities."""
+    import libjpeg_direct
+    if not libjpeg_direct.available():
+        pytest.skip("Pillow's libjpeg-turbo binary is not present")
+    from ffcv_b200.synthetic import synth_content
+    rng = np.random.default_rng(5)
+    for t in range(36):
+        h, w = int(rng.integers(1, 260)), int(rng.integers(1, 260))
+        img = rng.integers(0, 256, (h, w, 3), dtype=np.uint8) if t % 3 == 0 else synth_content(rng, h, w, 30.0)
+        buf = _encode(img, int(rng.choice([100, 95, 90, 50, 10])), [420, 444][t % 2], 0, t % 5 == 0)
+        for denom in (2, 4, 8):
+            want = libjpeg_direct.decode(buf, libjpeg_direct.JDCT_IFAST, True, denom)
+            assert np.array_equal(O.jpeg_decode_scaled(buf, denom), want), (t, denom)
