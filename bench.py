@@ -86,6 +86,8 @@ def parse_args():
     ap.add_argument('--no-cpu-baseline', action='store_true', help='skip the CPU oracle leg (profiling runs)')
     ap.add_argument('--no-configs', action='store_true', help='skip the short pass over the other configurations')
     ap.add_argument('--no-modes', action='store_true', help='skip the other staging modes (e2e_staged, e2e_gather, ...)')
+    ap.add_argument('--dct-downscale', action='store_true',
+                    help='decode JPEG samples at reduced scale where the crop allows (not the reference\'s pixels)')
     ap.add_argument('--batch', type=int, default=0, help='profiling runs: batch size instead of the configuration\'s')
     ap.add_argument('--kernels-only', action='store_true',
                     help='profiling runs: stage the slots once, then only re-run the kernels on one stream')
@@ -128,7 +130,7 @@ def distinct_images(cfg, args, world):
     return min(n, WORKLOADS[cfg]['samples'])
 
 
-def build_pipelines(cfg, device):
+def build_pipelines(cfg, device, dct_downscale=False):
     import torch as ch
     from ffcv_b200.fields.decoders import (CenterCropRGBImageDecoder, IntDecoder, RandomResizedCropRGBImageDecoder,
                                            SimpleRGBImageDecoder)
@@ -143,13 +145,15 @@ def build_pipelines(cfg, device):
         image = [RandomResizedCropRGBImageDecoder((160, 160), scale=(0.08, 1), ratio=(3 / 4, 4 / 3)),
                  RandomHorizontalFlip(), ToTensor(), ToDevice(device), ToTorchImage(), norm]
     elif cfg == 2:
-        image = [RandomResizedCropRGBImageDecoder((224, 224)), RandomHorizontalFlip(), ToTensor(), ToDevice(device),
+        image = [RandomResizedCropRGBImageDecoder((224, 224), dct_downscale=dct_downscale), RandomHorizontalFlip(),
+                 ToTensor(), ToDevice(device),
                  ToTorchImage(), norm]
     elif cfg == 3:
         image = [CenterCropRGBImageDecoder((256, 256), ratio=224 / 256), ToTensor(), ToDevice(device), ToTorchImage(),
                  norm]
     else:
-        image = [RandomResizedCropRGBImageDecoder((384, 384), scale=(0.25, 1)), RandomHorizontalFlip(), Cutout(64),
+        image = [RandomResizedCropRGBImageDecoder((384, 384), scale=(0.25, 1), dct_downscale=dct_downscale),
+                 RandomHorizontalFlip(), Cutout(64),
                  norm, ToTorchImage()]
     return {'image': image, 'label': [IntDecoder(), ToTensor(), ToDevice(device), Squeeze()]}
 
@@ -296,7 +300,7 @@ def run_oracle(batches, threads):
             ops.append(rec)
         t0 = time.perf_counter()
         _, status = O.run_batch(payloads, modes, h, w, params[:, :4], plan.resize, plan.out_h, plan.out_w, ops,
-                                plan.table, plan.out_kind, threads)
+                                plan.table, plan.out_kind, threads, dct_scale=plan.dct_scale)
         times.append(time.perf_counter() - t0)
         assert (status == 0).all()
     return times
@@ -389,7 +393,8 @@ class Bench:
         from ffcv_b200 import Loader, OrderOption
         w = WORKLOADS[cfg]
         return Loader(path, batch_size=w['batch'], order=getattr(OrderOption, w['order']), distributed=self.world > 1,
-                      seed=0, num_workers=self.workers, pipelines=build_pipelines(cfg, self.device),
+                      seed=0, num_workers=self.workers,
+                      pipelines=build_pipelines(cfg, self.device, self.args.dct_downscale),
                       batches_ahead=self.args.batches_ahead, drop_last=True, pin_file=pin, cpu_stage_share=share, **kw)
 
     @staticmethod
@@ -502,6 +507,8 @@ class Bench:
         self.barrier()
         path = dataset_path(cfg, images, args.restart_interval)
         out = {'config': config_dict(cfg, self.world, images, self.workers, args.restart_interval)}
+        if args.dct_downscale:
+            out['config']['dct_downscale'] = 'JPEG samples decoded at 1/2 .. 1/8 where the crop allows (opt-in: not the reference\'s pixels)'
 
         others = {}
         if full and not args.no_modes and not args.kernels_only:

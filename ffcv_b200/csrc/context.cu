@@ -303,6 +303,7 @@ bool valid_plan(const ffcvb_plan *p) {
         if (t != FFCVB_OP_FLIP && t != FFCVB_OP_TRANSLATE && t != FFCVB_OP_CUTOUT) return false;
         if (t != FFCVB_OP_FLIP && p->ops[k].arg < 0) return false;
     }
+    if (p->dct_scale < -1 || p->dct_scale > 3 || (p->dct_scale < 0 && !p->resize)) return false;
     return true;
 }
 
@@ -593,8 +594,28 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
                     }
                 }
                 d.nblocks = (uint32_t)d.bpm * d.mcus_x * d.mcu_rows;
+                // scale of the decode (plan->dct_scale): only layouts whose planes end up at one resolution
+                const bool scalable = h.ncomp == 3 && ((h.hs[0] == 1 && h.vs[0] == 1) || (h.hs[0] == 2 && h.vs[0] == 2));
+                int shift = 0;
+                if (plan->dct_scale > 0) {
+                    shift = plan->dct_scale;
+                    if (!scalable) d.host_status = (int16_t)kErrUnsupported;
+                } else if (plan->dct_scale < 0 && scalable) {
+                    const int32_t *p = params + (size_t)i * n_params;
+                    if (p[0] >= 0 && p[2] > 0 && p[0] + p[2] <= (int)d.height && p[1] >= 0 && p[3] > 0 &&
+                        p[1] + p[3] <= (int)d.width)
+                        while (shift < 3 && (p[2] >> (shift + 1)) >= plan->out_h && (p[3] >> (shift + 1)) >= plan->out_w) shift++;
+                }
+                d.scale_shift = (uint8_t)shift;
+                d.bs_luma = (uint8_t)(8 >> shift);
+                d.bs_chroma = (uint8_t)((8 >> shift) * h.hs[0] > 8 ? 8 : (8 >> shift) * h.hs[0]);
             }
+            d.dec_height = (uint16_t)((d.height + (1 << d.scale_shift) - 1) >> d.scale_shift);
+            d.dec_width = (uint16_t)((d.width + (1 << d.scale_shift) - 1) >> d.scale_shift);
+            if (d.bs_luma == 0) d.bs_luma = d.bs_chroma = 8; // rejected stream: fields stay consistent
         } else {
+            d.dec_height = d.height;
+            d.dec_width = d.width;
             int r0 = 0, rows = d.height, c0 = 0, cols = d.width;
             if (plan->resize) {
                 const int32_t *p = params + (size_t)i * n_params;
@@ -710,29 +731,32 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
         }
         for (int c = 0; c < h.ncomp; c++) {
             d.plane_off[c] = plane_bytes;
-            const size_t pw = (size_t)d.mcus_x * (c == 0 ? d.hs : 1) * 8;
-            const size_t ph = (size_t)d.mcus_y * (c == 0 ? d.vs : 1) * 8;
+            const size_t pw = (size_t)d.mcus_x * (c == 0 ? d.hs * d.bs_luma : d.bs_chroma);
+            const size_t ph = (size_t)d.mcus_y * (c == 0 ? d.vs * d.bs_luma : d.bs_chroma);
             plane_bytes += align_up(pw * ph, 16);
         }
         d.rgb_off = rgb_bytes;
-        rgb_bytes += align_up((size_t)d.height * d.width * 3, 16);
-        if ((int)d.height * d.width > max_pixels) max_pixels = (int)d.height * d.width;
+        rgb_bytes += align_up((size_t)d.dec_height * d.dec_width * 3, 16);
+        if ((int)d.dec_height * d.dec_width > max_pixels) max_pixels = (int)d.dec_height * d.dec_width;
         {   // extent the colour kernels' grids must cover: the crop box (plus the odd edge of a
             // chroma cell) where the kernel converts only that, else the whole image
-            int bw = d.width, bh = d.height;
+            int bw = d.dec_width, bh = d.dec_height;
             const bool boxed = d.ncomp == 3 && ((d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3) || (d.hs == 1 && d.vs == 1));
             if (plan->resize && boxed) {
                 const int32_t *p = params + (size_t)i * n_params;
                 if (p[0] >= 0 && p[2] > 0 && p[0] + p[2] <= (int)d.height && p[1] >= 0 && p[3] > 0 &&
                     p[1] + p[3] <= (int)d.width) {
-                    bw = p[3] + 2 < bw ? p[3] + 2 : bw;
-                    bh = p[2] + 2 < bh ? p[2] + 2 : bh;
+                    const int sw = (p[3] >> d.scale_shift) + 2, sh = (p[2] >> d.scale_shift) + 2; // the box at the decode's scale
+                    bw = sw < bw ? sw : bw;
+                    bh = sh < bh ? sh : bh;
                 }
             }
             if (bw > max_w) max_w = bw;
             if (bh > max_h) max_h = bh;
         }
-        if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3)
+        if (d.scale_shift != 0)
+            n_444++; // decoded at reduced scale: all planes at one resolution, no upsampling
+        else if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3)
             n_quad++;
         else if (d.ncomp == 3 && d.hs == 1 && d.vs == 1)
             n_444++;
@@ -843,6 +867,21 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     for (size_t k = 0; k < mult_src.size(); k++)
         build_mult_table(mult_src[k], reinterpret_cast<MultTable *>(s.host + hd.mult_off) + k);
     memcpy(s.host + hd.params_off, params, sizeof(int32_t) * (size_t)n * n_params);
+    for (int i = 0; i < n; i++) {
+        // a sample decoded at reduced scale: its crop box, for the kernels, is the box of the scaled
+        // image that covers it
+        const int sh = descs[i].scale_shift;
+        if (sh == 0 || !plan->resize) continue;
+        int32_t *p = reinterpret_cast<int32_t *>(s.host + hd.params_off) + (size_t)i * n_params;
+        const int r0 = p[0] >> sh, c0 = p[1] >> sh;
+        int r1 = (p[0] + p[2] + (1 << sh) - 1) >> sh, c1 = (p[1] + p[3] + (1 << sh) - 1) >> sh;
+        if (r1 > (int)descs[i].dec_height) r1 = descs[i].dec_height;
+        if (c1 > (int)descs[i].dec_width) c1 = descs[i].dec_width;
+        p[0] = r0;
+        p[1] = c0;
+        p[2] = r1 - r0;
+        p[3] = c1 - c0;
+    }
     for (const auto &r : s.riders) {
         if (!r.inline_bytes.empty()) {
             memcpy(s.host + r.off, r.inline_bytes.data(), r.bytes);
@@ -1372,23 +1411,29 @@ int imdecode(unsigned char *input_buffer, uint64_t input_size, uint32_t source_h
     (void)source_width;
     (void)offset_x;
     (void)offset_y;
-    // Every call the reference makes passes the identity transform (rgb_image.py:131-132,196-197).
-    if (enable_crop || hflip || scale_num != scale_denom || !input_buffer || !output_buffer) return -1;
+    // Every call the reference makes passes the identity transform and scale 1/1
+    // (rgb_image.py:131-132,196-197).  Scales 1/2, 1/4 and 1/8 are decoded too: as in the reference's
+    // call, the output then has TJSCALED(crop, scale) = ceil(crop * num / denom) pixels a side.
+    if (enable_crop || hflip || !input_buffer || !output_buffer || scale_num == 0 || scale_denom % scale_num != 0) return -1;
+    const uint32_t denom = scale_denom / scale_num;
+    if (denom != 1 && denom != 2 && denom != 4 && denom != 8) return -1;
+    const int shift = denom == 1 ? 0 : (denom == 2 ? 1 : (denom == 4 ? 2 : 3));
     std::lock_guard<std::mutex> g(g_mutex);
     ffcvb_ctx *ctx = global_ctx();
     if (!ctx) return -1;
     if (crop_height == 0 || crop_width == 0 || crop_height > 65535 || crop_width > 65535) return -1;
     ffcvb_plan plan{};
-    plan.out_h = (int32_t)crop_height;
-    plan.out_w = (int32_t)crop_width;
+    plan.out_h = (int32_t)((crop_height + denom - 1) / denom);
+    plan.out_w = (int32_t)((crop_width + denom - 1) / denom);
     plan.resize = 0;
+    plan.dct_scale = shift;
     plan.out_kind = FFCVB_OUT_U8_NHWC;
     const uint64_t ptr = 0, size = input_size;
     const uint8_t mode = FFCVB_MODE_JPG;
     const uint16_t hh = (uint16_t)crop_height, ww = (uint16_t)crop_width;
     const int32_t params[4] = {0, 0, (int32_t)crop_height, (int32_t)crop_width};
     if (ffcvb_stage_batch(ctx, 0, input_buffer, &ptr, &size, &mode, &hh, &ww, 1, &plan, params)) return -1;
-    const size_t out_bytes = (size_t)crop_height * crop_width * 3;
+    const size_t out_bytes = (size_t)plan.out_h * plan.out_w * 3;
     if (grow_dev(ctx, ctx->one_dst, out_bytes)) return -1;
     if (ffcvb_submit_batch(ctx, 0, nullptr, ctx->one_dst.p)) return -1;
     int32_t status = 0;

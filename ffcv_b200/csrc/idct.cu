@@ -41,6 +41,68 @@ __device__ __forceinline__ void idct8(int &v0, int &v1, int &v2, int &v3, int &v
     v3 = w16(t3 - t4);
 }
 
+// Reduced-size inverse transforms for decoding at 1/2, 1/4, 1/8 scale (the scale_num / scale_denom
+// arguments of libffcv/libffcv.cpp:59,89-90): a block goes straight to N x N samples, N = 8 / R, each
+// the mean of the R x R samples of the full transform it replaces.  Per dimension, in the scaling
+// of the integer transforms, the sum of R neighbouring outputs is
+//     S[m] = R a0 + sum_k a_k C(k, m),   C(k, m) = sqrt(2) sum_{j<R} cos((2 (R m + j) + 1) k pi / 16),
+// evaluated as libjpeg-turbo does: constants round(|C| 2^13), 32-bit sums, plain quantiser steps,
+// two extra fraction bits after the column pass, one rounding shift per pass that also divides by R.
+template <int R>
+__device__ __forceinline__ int reduced_constant(int k, int m) {
+    // C(k, m) * 2^13 for R = 2 (k = 4 contributes nothing) and R = 4 (only odd k contribute)
+    constexpr int c2[8][4] = {{0, 0, 0, 0},          {20995, 8697, -8697, -20995}, {15137, -15137, -15137, 15137},
+                              {7373, -17799, 17799, -7373}, {0, 0, 0, 0},          {-4926, 11893, -11893, 4926},
+                              {-6270, 6270, 6270, -6270},   {-4176, -1730, 1730, 4176}};
+    constexpr int c4[8][2] = {{0, 0}, {29692, -29692}, {0, 0}, {-10426, 10426}, {0, 0}, {6967, -6967}, {0, 0}, {-5906, 5906}};
+    return R == 2 ? c2[k][m & 3] : c4[k][m & 1];
+}
+
+template <int R>
+__device__ __forceinline__ void reduced_block(const int16_t *__restrict__ coef, const uint16_t *__restrict__ q,
+                                              uint8_t *__restrict__ dst, int pitch) {
+    constexpr int N = 8 / R, L = R == 2 ? 1 : 2;
+    int a[8][8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        const int4 cw = reinterpret_cast<const int4 *>(coef)[r];
+        const int4 qw = reinterpret_cast<const int4 *>(q)[r];
+        const int cc[4] = {cw.x, cw.y, cw.z, cw.w};
+        const int qq[4] = {qw.x, qw.y, qw.z, qw.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            a[r][2 * k] = (int)(short)(cc[k] & 0xffff) * (qq[k] & 0xffff);
+            a[r][2 * k + 1] = (cc[k] >> 16) * (int)((uint32_t)qq[k] >> 16);
+        }
+    }
+    int ws[8][N]; // [column of the block][row of the result]
+#pragma unroll
+    for (int col = 0; col < 8; col++)
+#pragma unroll
+        for (int m = 0; m < N; m++) {
+            int acc = a[0][col] * (1 << (13 + L));
+#pragma unroll
+            for (int k = 1; k < 8; k++) acc += a[k][col] * reduced_constant<R>(k, m);
+            ws[col][m] = (acc + (1 << (11 + L - 1))) >> (11 + L);
+        }
+#pragma unroll
+    for (int row = 0; row < N; row++) {
+        uint32_t packed = 0;
+#pragma unroll
+        for (int m = 0; m < N; m++) {
+            int acc = ws[0][row] * (1 << (13 + L));
+#pragma unroll
+            for (int k = 1; k < 8; k++) acc += ws[k][row] * reduced_constant<R>(k, m);
+            const int v = min(255, max(0, ((acc + (1 << (18 + L - 1))) >> (18 + L)) + 128));
+            packed |= (uint32_t)v << (8 * m);
+        }
+        if (N == 4)
+            *reinterpret_cast<uint32_t *>(dst + (size_t)row * pitch) = packed;
+        else
+            *reinterpret_cast<uint16_t *>(dst + (size_t)row * pitch) = (uint16_t)packed;
+    }
+}
+
 __device__ __forceinline__ int find_image(const ImageDesc *descs, const int32_t *list, int n_list,
                                           uint32_t blk) {
     // largest k with descs[list[k]].block_base <= blk (block_base ascends along the list)
@@ -70,18 +132,34 @@ idct_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ lis
     const int slot = (int)(b - mcu * d.bpm);
     const int my = mcu / d.mcus_x, mx = mcu - my * d.mcus_x;
     if (my < d.idct_row0 || mx < d.idct_col0 || mx >= d.idct_col1) return; // outside the crop's reach
-    int comp, bx, by, plane_w;
+    int comp, bx, by, plane_w, bs;
     if (d.ncomp == 1 || slot < luma) {
         comp = 0;
         const int v = slot / d.hs, h = slot - v * d.hs;
         bx = mx * d.hs + h;
         by = my * d.vs + v;
-        plane_w = d.mcus_x * d.hs * 8;
+        bs = d.bs_luma;
+        plane_w = d.mcus_x * d.hs * bs;
     } else {
         comp = slot - luma + 1;
         bx = mx;
         by = my;
-        plane_w = d.mcus_x * 8;
+        bs = d.bs_chroma;
+        plane_w = d.mcus_x * bs;
+    }
+    if (bs != 8) { // scaled decode: this block becomes bs x bs samples
+        const MultTable &mt = mult[d.q_tab[comp]];
+        const int16_t *cb = coef + (size_t)gb * 64;
+        uint8_t *dst = planes + d.plane_off[comp] + (size_t)(by * bs) * plane_w + bx * bs;
+        if (bs == 4) {
+            reduced_block<2>(cb, mt.q, dst, plane_w);
+        } else if (bs == 2) {
+            reduced_block<4>(cb, mt.q, dst, plane_w);
+        } else {
+            const int a0 = (int)cb[0] * (int)mt.q[0];
+            dst[0] = (uint8_t)min(255, max(0, ((a0 + 4) >> 3) + 128));
+        }
+        return;
     }
     const int16_t *q = mult[d.q_tab[comp]].m;
     const int4 *src = reinterpret_cast<const int4 *>(coef + (size_t)gb * 64);
@@ -161,7 +239,7 @@ color_quad_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict
                   const int32_t *__restrict__ params, int n_params) {
     const int img = list[blockIdx.z];
     const ImageDesc &d = descs[img];
-    if (d.host_status != 0 || d.ncomp != 3 || d.hs != 2 || d.vs != 2) return;
+    if (d.host_status != 0 || d.ncomp != 3 || d.hs != 2 || d.vs != 2 || d.scale_shift != 0) return;
     const int W = d.width, H = d.height;
     const int real_w = (W + 1) >> 1, real_h = (H + 1) >> 1;
     if (real_w < 3) return; // too narrow for the filter: the per-pixel kernel replicates
@@ -212,15 +290,16 @@ color_quad_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict
     }
 }
 
-// 4:4:4 images: no upsampling, one thread per pixel of the crop box, 2-D tiles (no divisions).
+// 4:4:4 images, and images decoded at reduced scale (whose chroma blocks were inverted to the luma
+// resolution): no upsampling, one thread per pixel of the crop box, 2-D tiles (no divisions).
 __global__ void __launch_bounds__(256)
 color_444_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
                  const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb,
                  const int32_t *__restrict__ params, int n_params) {
     const int img = list[blockIdx.z];
     const ImageDesc &d = descs[img];
-    if (d.host_status != 0 || d.ncomp != 3 || d.hs != 1 || d.vs != 1) return;
-    const int W = d.width, H = d.height;
+    if (d.host_status != 0 || d.ncomp != 3 || !(d.scale_shift != 0 || (d.hs == 1 && d.vs == 1))) return;
+    const int W = d.dec_width, H = d.dec_height;
     int x0 = 0, y0 = 0, x1 = W, y1 = H;
     if (params) {
         const int32_t *p = params + (size_t)img * n_params;
@@ -231,7 +310,7 @@ color_444_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict_
             x1 = p[1] + p[3];
         }
     }
-    const int pw = d.mcus_x * 8;
+    const int pw = d.mcus_x * d.hs * d.bs_luma; // = the chroma planes' pitch: all planes have one resolution here
     const uint8_t *Y = planes + d.plane_off[0], *Cb = planes + d.plane_off[1], *Cr = planes + d.plane_off[2];
     uint8_t *out = rgb + d.rgb_off;
     // every thread walks a column strip so that the grid stays small for very large images
@@ -259,6 +338,7 @@ color_other_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restric
     if (d.host_status != 0) return;
     const int W = d.width, H = d.height;
     const int real_w = (W + d.hs - 1) / d.hs, real_h = (H + d.vs - 1) / d.vs;
+    if (d.scale_shift != 0) return;                                      // equal-resolution kernel's
     if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && real_w >= 3) return; // quad kernel's
     if (d.ncomp == 3 && d.hs == 1 && d.vs == 1) return;                  // 4:4:4 kernel's
     const int npix = W * H;

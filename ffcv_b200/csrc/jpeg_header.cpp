@@ -174,6 +174,7 @@ void build_mult_table(const uint16_t quant[64], MultTable *out) {
         for (int c = 0; c < 8; c++) {
             int32_t s = (int32_t)(f[r] * f[c] * 16384.0 + 0.5);
             out->m[r * 8 + c] = (int16_t)(((int32_t)quant[r * 8 + c] * s + (1 << 11)) >> 12);
+            out->q[r * 8 + c] = quant[r * 8 + c];
         }
 }
 

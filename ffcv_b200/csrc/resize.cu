@@ -163,9 +163,9 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     bool ok = true;
     if (src.descs) {
         const ImageDesc &d = src.descs[i];
-        img_h = d.height;
-        img_w = d.width;
-        stride = d.width * 3;
+        img_h = d.dec_height; // the decoded size: smaller than the stored one after a scaled decode
+        img_w = d.dec_width;
+        stride = d.dec_width * 3;
         if (d.mode == 1) {
             base = src.blob + d.payload_off;
             row0 = d.row0;

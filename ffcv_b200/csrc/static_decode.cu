@@ -94,8 +94,9 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     memset(&m, 0, sizeof(m));
     ImageDesc &d = m.desc;
     d.payload_size = (uint32_t)jpeg_size;
-    d.height = (uint16_t)height;
-    d.width = (uint16_t)width;
+    d.height = d.dec_height = (uint16_t)height;
+    d.width = d.dec_width = (uint16_t)width;
+    d.bs_luma = d.bs_chroma = 8; // full scale
     d.scan_off = (uint32_t)h.scan_off;
     d.scan_len = (uint32_t)h.scan_len;
     d.ncomp = (uint8_t)h.ncomp;

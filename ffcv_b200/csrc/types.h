@@ -30,6 +30,13 @@ struct ImageDesc {
     uint8_t q_tab[kMaxComponents];                          // indices into the batch's MultTable array
     uint8_t raw_skew;      // raw, gathered row by row: row r of the staged payload starts
                            // (src_addr + r * width * 3) & 15 bytes into its raw_pitch-wide slot
+    // Decoding at reduced scale (1 / 2^scale_shift, JPEG only): every block of a component is
+    // inverted straight to bs x bs samples (8 at full scale), and the decoded image has
+    // dec_height x dec_width = ceil(height / 2^s) x ceil(width / 2^s) pixels.  With 2x2 chroma
+    // subsampling the chroma blocks use twice the luma's bs (at most 8), so all planes of a scaled
+    // image have the same resolution.  dec_* equal height / width for unscaled and raw samples.
+    uint8_t scale_shift, bs_luma, bs_chroma;
+    uint16_t dec_height, dec_width;
     // The crop box decides how much of the image is needed: the entropy decoder stops after
     // `mcu_rows` rows of MCUs and the inverse transform runs only on the MCUs of the box below
     // (the crop box grown by the reach of the chroma filter).  Whole image when there is no crop.
@@ -75,9 +82,11 @@ inline uint16_t huff_entry(int len, int sym) {
     return (uint16_t)((len + s) | (s << 5) | (dz << 9));
 }
 
-// Dequantisation multipliers of the fast integer IDCT: quantiser step x AAN scale, 2 fraction bits.
+// Dequantisation multipliers of the fast integer IDCT: quantiser step x AAN scale, 2 fraction bits;
+// and the plain quantiser steps, which the reduced-size transforms of a scaled decode use.
 struct MultTable {
     int16_t m[64];
+    uint16_t q[64];
 };
 
 struct BatchHeader {

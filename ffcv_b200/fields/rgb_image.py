@@ -96,18 +96,29 @@ class SimpleRGBImageDecoder(Operation):
 
 
 class ResizedCropRGBImageDecoder(SimpleRGBImageDecoder, metaclass=ABCMeta):
-    """Crop then INTER_AREA-resize to ``output_size`` (reference: rgb_image.py:142-217)."""
+    """Crop then INTER_AREA-resize to ``output_size`` (reference: rgb_image.py:142-217).
 
-    def __init__(self, output_size):
+    ``dct_downscale`` (not in the reference, off by default): decode a JPEG sample at 1/2, 1/4 or 1/8
+    scale -- the ``scale_num / scale_denom`` of the reference's ``imdecode``
+    (libffcv/libffcv.cpp:59,89-90), which its decoders always leave at 1/1 -- whenever the sample's
+    crop box still has at least ``output_size`` pixels at that scale, and resize from the scaled
+    image.  The scaled decode equals libjpeg-turbo's bit for bit, but a crop resized from it is not
+    the crop resized from the full decode, so the pixels are no longer the reference's."""
+
+    def __init__(self, output_size, dct_downscale=False):
         super().__init__()
         self.output_size = output_size
+        self.dct_downscale = bool(dct_downscale)
 
     def output_shape(self):
         return int(self.output_size[0]), int(self.output_size[1])
 
     def fuse(self, plan) -> bool:
         h, w = self.output_shape()
-        return plan.set_decoder(self, h, w, resize=True)
+        if not plan.set_decoder(self, h, w, resize=True):
+            return False
+        plan.dct_scale = -1 if self.dct_downscale else 0
+        return True
 
     @property
     @abstractmethod
@@ -128,8 +139,8 @@ class RandomResizedCropRGBImageDecoder(ResizedCropRGBImageDecoder):
         The range of potential aspect ratios that can be randomly sampled
     """
 
-    def __init__(self, output_size, scale=(0.08, 1.0), ratio=(0.75, 4 / 3)):
-        super().__init__(output_size)
+    def __init__(self, output_size, scale=(0.08, 1.0), ratio=(0.75, 4 / 3), dct_downscale=False):
+        super().__init__(output_size, dct_downscale)
         self.scale = scale
         self.ratio = ratio
 
@@ -154,8 +165,8 @@ class CenterCropRGBImageDecoder(ResizedCropRGBImageDecoder):
         ratio of (crop size) / (min side length)
     """
 
-    def __init__(self, output_size, ratio):
-        super().__init__(output_size)
+    def __init__(self, output_size, ratio, dct_downscale=False):
+        super().__init__(output_size, dct_downscale)
         self.scale = None
         self.ratio = ratio
 

@@ -34,7 +34,7 @@ class Op(Structure):
 
 class Plan(Structure):
     _fields_ = [('out_h', c_int32), ('out_w', c_int32), ('resize', c_int32), ('out_kind', c_int32),
-                ('n_ops', c_int32), ('ops', Op * MAX_OPS), ('lut_dev', c_void_p)]
+                ('n_ops', c_int32), ('ops', Op * MAX_OPS), ('dct_scale', c_int32), ('lut_dev', c_void_p)]
 
 
 class Rider(Structure):
@@ -114,8 +114,9 @@ def imdecode_static(jpeg_host: np.ndarray, jpeg_dev_ptr: int, height: int, width
                                      rgb_dev_ptr, stream or None)
 
 
-def make_plan(out_h, out_w, resize, out_kind, ops=(), lut_dev=0):
-    """ops: sequence of (type, arg, fill) with fill a 3-sequence of ints."""
+def make_plan(out_h, out_w, resize, out_kind, ops=(), lut_dev=0, dct_scale=0):
+    """ops: sequence of (type, arg, fill) with fill a 3-sequence of ints.  dct_scale: 0 full-scale
+    decode, 1..3 every JPEG at 1/2, 1/4, 1/8, -1 per sample by its crop box (see ffcvb_plan)."""
     if len(ops) > MAX_OPS:
         raise ValueError(f'at most {MAX_OPS} fused augmentations')
     plan = Plan()
@@ -128,6 +129,7 @@ def make_plan(out_h, out_w, resize, out_kind, ops=(), lut_dev=0):
         plan.ops[k].arg = int(arg)
         for c in range(3):
             plan.ops[k].fill[c] = int(fill[c]) & 255
+    plan.dct_scale = int(dct_scale)
     plan.lut_dev = int(lut_dev) if lut_dev else None
     return plan
 

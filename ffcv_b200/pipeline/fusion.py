@@ -20,6 +20,7 @@ class FusedImagePlan:
         self.crop_sampler = None  # operation that draws the crop boxes when it is not the decoder
         self.out_h = self.out_w = None
         self.resize = False
+        self.dct_scale = 0        # scale of the JPEG decode (ffcvb_plan.dct_scale): 0 full, -1 by crop box
         self.ops = []             # (native type, arg, fill, operation) in pipeline order
         self.device = None        # set by ToDevice; defaults to the current CUDA device
         self.table = None         # 256 x 3 lookup table of the output type (numpy), or None
@@ -149,7 +150,8 @@ class FusedImageExecutor:
         ops = [(t, a, f) for (t, a, f, _) in plan.ops]
         self.native_plan = L.make_plan(plan.out_h, plan.out_w, plan.resize, L.OUT_U8_NHWC if plan.needs_repack()
                                        else plan.out_kind, ops,
-                                       self.table_dev.data_ptr() if self.table_dev is not None else 0)
+                                       self.table_dev.data_ptr() if self.table_dev is not None else 0,
+                                       dct_scale=plan.dct_scale)
         self.n_params = 4 + 2 * len(ops)
         self.last_params = None
         self._prepared = None     # ((epoch, batch, n), arrays) drawn ahead for the next batch

@@ -78,6 +78,16 @@ typedef struct {
     int32_t out_kind;     /* FFCVB_OUT_* */
     int32_t n_ops;
     ffcvb_op ops[FFCVB_MAX_OPS];
+    int32_t dct_scale;    /* decode JPEG samples at reduced scale, the scale_num / scale_denom of
+                             libffcv/libffcv.cpp:59,89-90 (which every call of the reference sets to
+                             1 / 1): 0 = full scale (default); 1, 2, 3 = every JPEG sample at 1/2,
+                             1/4, 1/8 (samples whose chroma layout does not allow it are flagged);
+                             -1 (needs resize == 1) = per sample the smallest scale at which its
+                             crop box still has at least out_h x out_w pixels, then the box is
+                             mapped to the scaled image (rows [i >> s, ceil((i + h) / 2^s)), same for
+                             columns) and resized from there.  Scaled decodes equal libjpeg-turbo's
+                             bit for bit, but a crop resized from a scaled decode is not the crop
+                             resized from the full decode: not the reference's pixels, hence opt-in. */
     const void *lut_dev; /* DEVICE pointer to the 256 x 3 normalisation table of the output type
                             (ffcv/transforms/normalize.py:42-49); unused for FFCVB_OUT_U8_NHWC */
 } ffcvb_plan;

@@ -738,8 +738,9 @@ int oracle_jpeg_decode_scaled(const uint8_t *data, size_t n, uint8_t *out, int o
 
 /* Same signature as libffcv/libffcv.cpp:53-61 `imdecode`.  The crop and flip arguments must be
  * the identity, as in every call the reference makes (fields/rgb_image.py:131-132,196-197); the
- * scale may be 1/1 (what the reference passes) or 1/2, 1/4, 1/8, in which case crop_height /
- * crop_width are the scaled dimensions, as TurboJPEG expects them. */
+ * scale may be 1/1 (what the reference passes) or 1/2, 1/4, 1/8: crop_height / crop_width stay
+ * the stream's dimensions and the output has TJSCALED(dim, scale) = ceil(dim * num / denom) pixels
+ * a side, as in the reference's tjDecompress2 call (libffcv.cpp:104-106). */
 int imdecode(unsigned char *input_buffer, uint64_t input_size, uint32_t source_height,
              uint32_t source_width, unsigned char *output_buffer, uint32_t crop_height,
              uint32_t crop_width, uint32_t offset_x, uint32_t offset_y, uint32_t scale_num,
@@ -755,8 +756,9 @@ int imdecode(unsigned char *input_buffer, uint64_t input_size, uint32_t source_h
         rc = oracle_jpeg_decode(input_buffer, (size_t)input_size, output_buffer, (int)crop_height,
                                 (int)crop_width, IDCT_FAST, UPSAMPLE_FANCY);
     else
-        rc = oracle_jpeg_decode_scaled(input_buffer, (size_t)input_size, output_buffer, (int)crop_height,
-                                       (int)crop_width, (int)denom);
+        rc = oracle_jpeg_decode_scaled(input_buffer, (size_t)input_size, output_buffer,
+                                       (int)((crop_height + denom - 1) / denom), (int)((crop_width + denom - 1) / denom),
+                                       (int)denom);
     return rc ? -1 : 0;
 }
 

@@ -151,9 +151,10 @@ def normalize_table(mean, std, dtype):
 
 
 def run_batch(payloads, modes, heights, widths, crops, resize, out_h, out_w, ops_per_sample, lut,
-              out_kind, nthreads=1):
+              out_kind, nthreads=1, dct_scale=0):
     """Whole path for a batch.  payloads: list of uint8 arrays; crops: [n, 4] (i, j, h, w);
-    ops_per_sample: list (per sample) of op records; lut: 256x3 table or None."""
+    ops_per_sample: list (per sample) of op records; lut: 256x3 table or None; dct_scale: 0 = JPEG
+    samples decoded at full scale, 1..3 = at 1/2, 1/4, 1/8, -1 = per sample by its crop box."""
     n = len(payloads)
     payloads = [np.ascontiguousarray(p, dtype=np.uint8) for p in payloads]
     ptrs = (ctypes.c_void_p * n)(*[p.ctypes.data for p in payloads])
@@ -163,7 +164,7 @@ def run_batch(payloads, modes, heights, widths, crops, resize, out_h, out_w, ops
     desc[:, 1] = heights
     desc[:, 2] = widths
     desc[:, 3:7] = crops
-    desc[:, 7] = int(bool(resize))
+    desc[:, 7] = int(bool(resize)) | ((255 if dct_scale < 0 else int(dct_scale)) << 8)
     nops = len(ops_per_sample[0]) if n else 0
     ops = np.zeros((n, max(nops, 1), 8), dtype=np.int32)
     for i in range(n):

@@ -18,6 +18,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+int oracle_jpeg_scalable(const uint8_t *data, size_t n);
+int oracle_jpeg_decode_scaled(const uint8_t *data, size_t n, uint8_t *out, int out_h, int out_w, int denom);
 int oracle_jpeg_decode(const uint8_t *data, size_t n, uint8_t *out, int height, int width,
                        int idct, int upsample);
 void oracle_resize_area(const uint8_t *src, int src_cols, int r0, int r1, int c0, int c1,
@@ -87,7 +89,10 @@ typedef struct {
     int n;
     const uint8_t *const *payloads;
     const uint64_t *sizes;
-    const int32_t *desc; /* [n][8]: mode (0 jpg, 1 raw), h, w, crop i, crop j, crop h, crop w, resize? */
+    const int32_t *desc; /* [n][8]: mode (0 jpg, 1 raw), h, w, crop i, crop j, crop h, crop w,
+                            flags: bit 0 resize?; bits 8-15 scale of the JPEG decode: 0 full, 1..3 =
+                            1/2, 1/4, 1/8, 255 = per sample, the smallest scale at which the crop
+                            box keeps at least oh x ow pixels */
     int oh, ow;
     const int32_t *ops; /* [n][nops][8] */
     int nops;
@@ -106,9 +111,35 @@ static void run_sample(Job *j, int i) {
     uint8_t *decoded = NULL;
     const uint8_t *pix;
     j->status[i] = 0;
+    int oh = j->oh, ow = j->ow;
+    int ci = d[3], cj = d[4], chh = d[5], cww = d[6];
+    const int resize = d[7] & 1, scale_mode = (d[7] >> 8) & 255;
     if (mode == 0) {
-        decoded = (uint8_t *)malloc((size_t)h * w * 3);
-        int rc = oracle_jpeg_decode(j->payloads[i], (size_t)j->sizes[i], decoded, h, w, 0, 0);
+        int shift = 0;
+        if (scale_mode >= 1 && scale_mode <= 3) {
+            shift = scale_mode;
+        } else if (scale_mode == 255 && resize && oracle_jpeg_scalable(j->payloads[i], (size_t)j->sizes[i])) {
+            while (shift < 3 && (chh >> (shift + 1)) >= oh && (cww >> (shift + 1)) >= ow) shift++;
+        }
+        int rc;
+        if (shift == 0) {
+            decoded = (uint8_t *)malloc((size_t)h * w * 3);
+            rc = oracle_jpeg_decode(j->payloads[i], (size_t)j->sizes[i], decoded, h, w, 0, 0);
+        } else {
+            /* decode at 1 / 2^shift; the crop box becomes the box of the scaled image that covers it */
+            const int sh = (h + (1 << shift) - 1) >> shift, sw = (w + (1 << shift) - 1) >> shift;
+            decoded = (uint8_t *)malloc((size_t)sh * sw * 3);
+            rc = oracle_jpeg_decode_scaled(j->payloads[i], (size_t)j->sizes[i], decoded, sh, sw, 1 << shift);
+            int r1 = (ci + chh + (1 << shift) - 1) >> shift, c1 = (cj + cww + (1 << shift) - 1) >> shift;
+            if (r1 > sh) r1 = sh;
+            if (c1 > sw) c1 = sw;
+            ci >>= shift;
+            cj >>= shift;
+            chh = r1 - ci;
+            cww = c1 - cj;
+            h = sh;
+            w = sw;
+        }
         if (rc) {
             j->status[i] = rc;
             free(decoded);
@@ -118,10 +149,9 @@ static void run_sample(Job *j, int i) {
     } else {
         pix = j->payloads[i];
     }
-    int oh = j->oh, ow = j->ow;
     uint8_t *img = (uint8_t *)malloc((size_t)oh * ow * 3);
-    if (d[7])
-        oracle_resize_area(pix, w, d[3], d[3] + d[5], d[4], d[4] + d[6], img, oh, ow);
+    if (resize)
+        oracle_resize_area(pix, w, ci, ci + chh, cj, cj + cww, img, oh, ow);
     else
         memcpy(img, pix, (size_t)oh * ow * 3);
     int pad = 0;

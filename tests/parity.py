@@ -43,7 +43,7 @@ def oracle_batch(loader, executor, batch_indices, params, nthreads=4):
         ops.append(rec)
     kind = executor.native_plan.out_kind
     out, status = O.run_batch(payloads, md['mode'], md['height'], md['width'], params[:, :4], plan.resize,
-                              plan.out_h, plan.out_w, ops, plan.table, kind, nthreads)
+                              plan.out_h, plan.out_w, ops, plan.table, kind, nthreads, dct_scale=plan.dct_scale)
     assert (status == 0).all(), status
     return out
 

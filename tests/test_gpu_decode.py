@@ -170,3 +170,33 @@ def test_my_fread(tmp_path):
     lib.my_fread(fp, 1234, out.ctypes.data, out.size)
     libc.fclose(fp)
     assert np.array_equal(out, data[1234:1234 + 777])
+
+
+@pytest.mark.parametrize('case', [c for c in CASES if c[3] != 422],
+                         ids=lambda c: f'{c[0]}x{c[1]}q{c[2]}s{c[3]}r{c[4]}o{c[5]}{c[6]}')
+def test_imdecode_scaled_bit_exact(case):
+    """`imdecode(..., scale_num, scale_denom)` at 1/2, 1/4 and 1/8 (libffcv/libffcv.cpp:59,89-90,104:
+    the output has TJSCALED(dim) = ceil(dim / denom) pixels a side) against the oracle and against
+    libjpeg-turbo's own scaled decode with the fast integer IDCT selected: bit-exact."""
+    import libjpeg_direct
+    from ffcv_b200.libffcv import imdecode
+    h, w, q, samp, rst, opt, kind = case
+    rng = np.random.default_rng(h * 10007 + w)
+    buf = _encode(_content(rng, h, w, kind), q, samp, rst, opt)
+    for denom in (2, 4, 8):
+        sh, sw = -(-h // denom), -(-w // denom)
+        got = np.zeros((sh, sw, 3), dtype=np.uint8)
+        assert imdecode(buf, got, h, w, h, w, 0, 0, 1, denom, False, False) == 0
+        assert np.array_equal(got, O.jpeg_decode_scaled(buf, denom)), denom
+        if libjpeg_direct.available():
+            assert np.array_equal(got, libjpeg_direct.decode(buf, libjpeg_direct.JDCT_IFAST, True, denom)), denom
+
+
+def test_imdecode_scaled_refuses_what_it_cannot_scale():
+    from ffcv_b200.libffcv import imdecode
+    rng = np.random.default_rng(9)
+    img = _content(rng, 64, 80, 'smooth')
+    got = np.zeros((32, 40, 3), dtype=np.uint8)
+    assert imdecode(_encode(img, 90, 422), got, 64, 80, 64, 80, 0, 0, 1, 2) == -1   # 4:2:2
+    assert imdecode(_encode(img, 90), got, 64, 80, 64, 80, 0, 0, 1, 3) == -1         # 1/3 is not offered
+    assert imdecode(_encode(img, 90), got, 64, 80, 64, 80, 0, 0, 1, 2) == 0

@@ -440,3 +440,31 @@ def test_larger_than_ram_path_reads_straight_into_pinned_buffers(tmp_path, direc
     # On a file system that can drop clean pages (not tmpfs) an epoch leaves the cache as it found it.
     if before is not None and after is not None and before < 0.5:
         assert after < before + 0.15, (before, after)
+
+
+@pytest.mark.parametrize('cfg,res,batch', [(4, 384, 3), (2, 96, 32), (1, 48, 64)])
+def test_dct_domain_downscale_option(datasets, cfg, res, batch):
+    """`dct_downscale=True`: JPEG samples whose crop box is at least twice the output size are
+    decoded at 1/2, 1/4 or 1/8 scale and resized from the scaled image; raw samples and small crops
+    are untouched.  Checked against the oracle, which applies the same rule with its own scaled
+    decode (pinned on libjpeg-turbo's)."""
+    from ffcv_b200 import OrderOption
+    from ffcv_b200.fields.decoders import RandomResizedCropRGBImageDecoder
+    from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, ToTorchImage
+    pipes = {'image': [RandomResizedCropRGBImageDecoder((res, res), scale=(0.25, 1), dct_downscale=True),
+                       RandomHorizontalFlip(), NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()],
+             'label': None}
+    loader = _loader(datasets[cfg], batch, pipes, order=OrderOption.QUASI_RANDOM)
+    exe = image_executor(loader)
+    assert exe.plan.dct_scale == -1
+    compare_epoch(loader)
+    # the rule did select reduced scales for part of the samples
+    p = exe.last_params
+    assert ((p[:, 2] >> 1) >= res).any() and ((p[:, 3] >> 1) >= res).any()
+    # and the result is not the full-scale pipeline's (the option changes pixels: it is opt-in)
+    plain = {'image': [RandomResizedCropRGBImageDecoder((res, res), scale=(0.25, 1)), RandomHorizontalFlip(),
+                       NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()], 'label': None}
+    a = next(iter(_loader(datasets[cfg], batch, pipes, order=OrderOption.QUASI_RANDOM)))[0]
+    b = next(iter(_loader(datasets[cfg], batch, plain, order=OrderOption.QUASI_RANDOM)))[0]
+    assert a.shape == b.shape and not ch.equal(a, b)
+    assert (a.float() - b.float()).abs().mean() < 0.1  # same picture, different rounding path
