@@ -143,6 +143,14 @@ class Pool {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// FNV-1a over a table's bytes: lets the (serial) table deduplication of a batch compare 8 bytes
+// per table instead of the tables themselves; the hashes are computed by the parallel header parse.
+uint64_t hash_bytes(const void *p, size_t n, uint64_t h = 1469598103934665603ull) {
+    const uint8_t *b = static_cast<const uint8_t *>(p);
+    for (size_t i = 0; i < n; i++) h = (h ^ b[i]) * 1099511628211ull;
+    return h;
+}
+
 // Copy into the pinned staging buffer with non-temporal stores: the destination is read next by
 // the DMA engine, not by the CPU, so it should not displace the cache or cost a read-for-ownership.
 // dst is 16-byte aligned (payload offsets are).
@@ -198,6 +206,7 @@ struct Slot {
     std::vector<Rider> pending_riders, riders; // set for the next staging / staged with the current batch
     double stage_ms[4] = {0, 0, 0, 0}; // header parse, layout, payload copy, total
     std::vector<JpegHeader> headers;
+    std::vector<uint64_t> table_hash; // per sample: hashes of its (DC, AC, quantisation) tables x 3 components
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     // payload gather runs on its own high-priority stream so that its few CTAs are placed ahead of
     // the large grids other slots have queued, and the PCIe transfer overlaps their compute
@@ -487,6 +496,7 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     descs.assign(n, ImageDesc{});
     s.src_ptrs.assign(ptrs, ptrs + n);
     s.headers.resize(n);
+    s.table_hash.assign((size_t)n * 9, 0);
 
     // ---- reading from file descriptors: every sample's bytes get their place in the pinned buffer
     // before anything is parsed (a JPEG header can only be parsed once it has been read), so the
@@ -594,6 +604,12 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
                     }
                 }
                 d.nblocks = (uint32_t)d.bpm * d.mcus_x * d.mcu_rows;
+                for (int c = 0; c < h.ncomp; c++) {
+                    uint64_t *th = &s.table_hash[(size_t)i * 9 + 3 * c];
+                    th[0] = hash_bytes(h.dc[h.td[c]].vals, 256, hash_bytes(h.dc[h.td[c]].bits, 17));
+                    th[1] = hash_bytes(h.ac[h.ta[c]].vals, 256, hash_bytes(h.ac[h.ta[c]].bits, 17));
+                    th[2] = hash_bytes(h.quant[h.tq[c]], 128);
+                }
                 // scale of the decode (plan->dct_scale): only layouts whose planes end up at one resolution
                 const bool scalable = h.ncomp == 3 && ((h.hs[0] == 1 && h.vs[0] == 1) || (h.hs[0] == 2 && h.vs[0] == 2));
                 int shift = 0;
@@ -680,6 +696,7 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     // ---- serial: deduplicate tables, lay the blob out
     std::vector<const RawHuff *> huff_src;
     std::vector<const uint16_t *> mult_src;
+    std::vector<uint64_t> huff_hash, mult_hash;
     std::vector<int32_t> jpeg_list, par_list, seq_list;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes_par = 0;  // scan_bytes_par: largest scan
     uint32_t total_blocks = 0;
@@ -697,24 +714,27 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
         for (int c = 0; c < h.ncomp; c++) {
             const RawHuff *tabs[2] = {&h.dc[h.td[c]], &h.ac[h.ta[c]]};
             uint8_t *dst[2] = {&d.dc_tab[c], &d.ac_tab[c]};
+            const uint64_t *th = &s.table_hash[(size_t)i * 9 + 3 * c];
             for (int k = 0; k < 2; k++) {
+                // same 64-bit hash and same code-length counts: taken to be the same table
                 int found = -1;
                 for (int u = (int)huff_src.size() - 1; u >= 0 && found < 0; u--)
-                    if (huff_src[u] == tabs[k] || (memcmp(huff_src[u]->bits, tabs[k]->bits, 17) == 0 &&
-                                                   memcmp(huff_src[u]->vals, tabs[k]->vals, 256) == 0))
+                    if (huff_hash[u] == th[k] && (huff_src[u] == tabs[k] || memcmp(huff_src[u]->bits, tabs[k]->bits, 17) == 0))
                         found = u;
                 if (found < 0) {
                     found = (int)huff_src.size();
                     huff_src.push_back(tabs[k]);
+                    huff_hash.push_back(th[k]);
                 }
                 *dst[k] = (uint8_t)found;
             }
             int qfound = -1;
             for (int u = (int)mult_src.size() - 1; u >= 0 && qfound < 0; u--)
-                if (memcmp(mult_src[u], h.quant[h.tq[c]], 128) == 0) qfound = u;
+                if (mult_hash[u] == th[2] && mult_src[u][0] == h.quant[h.tq[c]][0]) qfound = u;
             if (qfound < 0) {
                 qfound = (int)mult_src.size();
                 mult_src.push_back(h.quant[h.tq[c]]);
+                mult_hash.push_back(th[2]);
             }
             d.q_tab[c] = (uint8_t)qfound;
         }
