@@ -5,6 +5,7 @@
 #include <errno.h>
 #include <fcntl.h>
 #include <stdarg.h>
+#include <stddef.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -143,12 +144,23 @@ class Pool {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// FNV-1a over a table's bytes: lets the (serial) table deduplication of a batch compare 8 bytes
-// per table instead of the tables themselves; the hashes are computed by the parallel header parse.
-uint64_t hash_bytes(const void *p, size_t n, uint64_t h = 1469598103934665603ull) {
+// Multiplicative hash over a table's bytes, eight at a time: lets the (serial) table
+// deduplication of a batch compare 8 bytes per table instead of the tables themselves; the hashes
+// are computed by the parallel header parse.
+uint64_t hash_bytes(const void *p, size_t n) {
     const uint8_t *b = static_cast<const uint8_t *>(p);
-    for (size_t i = 0; i < n; i++) h = (h ^ b[i]) * 1099511628211ull;
-    return h;
+    uint64_t h = 0x9E3779B97F4A7C15ull ^ n;
+    size_t i = 0;
+    for (; i + 8 <= n; i += 8) {
+        uint64_t w;
+        memcpy(&w, b + i, 8);
+        h = (h ^ w) * 0xFF51AFD7ED558CCDull;
+        h ^= h >> 29;
+    }
+    uint64_t w = 0;
+    if (i < n) memcpy(&w, b + i, n - i);
+    h = (h ^ w) * 0xC4CEB9FE1A85EC53ull;
+    return h ^ (h >> 32);
 }
 
 // Copy into the pinned staging buffer with non-temporal stores: the destination is read next by
@@ -606,8 +618,10 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
                 d.nblocks = (uint32_t)d.bpm * d.mcus_x * d.mcu_rows;
                 for (int c = 0; c < h.ncomp; c++) {
                     uint64_t *th = &s.table_hash[(size_t)i * 9 + 3 * c];
-                    th[0] = hash_bytes(h.dc[h.td[c]].vals, 256, hash_bytes(h.dc[h.td[c]].bits, 17));
-                    th[1] = hash_bytes(h.ac[h.ta[c]].vals, 256, hash_bytes(h.ac[h.ta[c]].bits, 17));
+                    // (bits[17] and vals[256] lie next to each other in RawHuff)
+                    static_assert(offsetof(RawHuff, vals) == 17, "RawHuff: vals must follow bits");
+                    th[0] = hash_bytes(h.dc[h.td[c]].bits, 17 + 256);
+                    th[1] = hash_bytes(h.ac[h.ta[c]].bits, 17 + 256);
                     th[2] = hash_bytes(h.quant[h.tq[c]], 128);
                 }
                 // scale of the decode (plan->dct_scale): only layouts whose planes end up at one resolution
