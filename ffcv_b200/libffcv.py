@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_HERE, 'libffcv_b200.so')
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m ffcv_b200._build` (needs nvcc). "
+        f"{LIB_PATH} is missing: build it with `python ffcv_b200/_build.py` (needs nvcc). "
         "ffcv_b200 has no CPU fallback.")
 
 lib = CDLL(LIB_PATH)
