@@ -262,8 +262,9 @@ struct ffcvb_ctx {
     double share = 0.0;          // the adjusted share, 0..1
     int split_copy_threads = 4; // ... and how many of them copy at a time (more only crowd the gather out)
     // Tuning overrides, read from the environment once when the context is created (0 = none):
-    // FFCV_B200_COPY_THREADS, FFCV_B200_SUBSEQ_BITS, FFCV_B200_ENTROPY_THREADS, FFCV_B200_GATHER_CTAS.
-    int tune_copy_threads = 0, tune_subseq_bits = 0, tune_entropy_threads = 0, gather_ctas = 0;
+    // FFCV_B200_COPY_THREADS, FFCV_B200_SUBSEQ_BITS, FFCV_B200_ENTROPY_THREADS, FFCV_B200_GATHER_CTAS,
+    // FFCV_B200_GATHER_IN_FLIGHT.
+    int tune_copy_threads = 0, tune_subseq_bits = 0, tune_entropy_threads = 0, gather_ctas = 0, gather_in_flight = 8;
     DevBuf one_src, one_dst; // single-image entry points
 };
 
@@ -393,6 +394,7 @@ int ffcvb_create(int device, int n_slots, int n_threads, ffcvb_ctx **out) {
         c->tune_entropy_threads != 1024)
         c->tune_entropy_threads = 0; // only the CTA sizes the kernel is built for
     c->gather_ctas = env_int("FFCV_B200_GATHER_CTAS", 1, 1024);
+    if (env_int("FFCV_B200_GATHER_IN_FLIGHT", 4, 4)) c->gather_in_flight = 4;
     *out = c;
     return FFCVB_OK;
 }
@@ -1097,7 +1099,7 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         CU(cudaMemcpyAsync(blob, s.host, hd.payload_off, cudaMemcpyHostToDevice, s.gather_stream));
         CU(cudaEventRecord(s.ev_gather_start, s.gather_stream)); // after the head's copy: that one queues behind other batches' transfers
         s.gather_timed = true;
-        launch_gather_payloads(reinterpret_cast<const ImageDesc *>(blob + hd.desc_off), s.n, blob, ctx->gather_ctas, s.gather_stream);
+        launch_gather_payloads(reinterpret_cast<const ImageDesc *>(blob + hd.desc_off), s.n, blob, ctx->gather_ctas, ctx->gather_in_flight, s.gather_stream);
         CU(cudaEventRecord(s.ev_gathered, s.gather_stream));
         if (s.staged_end > hd.payload_off) { // the CPU-staged share rides the copy engine meanwhile
             if ((hrc = hold_for_copy(ctx, s, st))) return hrc;

@@ -4,9 +4,11 @@
 
 namespace ffcvb {
 
-// 16 CTAs of 256 threads with four 16-byte loads in flight each (256 KB outstanding) already fill
-// the PCIe link (51 GB/s measured); more outstanding system-memory reads only congest the memory
-// system for the decode kernels running beside it (48 x 512 threads halved a concurrent HBM copy).
+// 16 CTAs of 256 threads with eight 16-byte loads in flight each (512 KB outstanding) move 43-44
+// GB/s inside the loader's pipeline (four in flight: 43.0, eight: 44.0; a single pinned DMA copy:
+// 55); more CTAs are slower (32: 38.9 GB/s, 8: 42.3): more outstanding system-memory reads only
+// congest the memory system for the decode kernels running beside it.
+template <int kInFlight>
 __global__ void __launch_bounds__(256)
 gather_payloads_kernel(const ImageDesc *__restrict__ descs, int n, uint8_t *__restrict__ blob) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -67,23 +69,26 @@ gather_payloads_kernel(const ImageDesc *__restrict__ descs, int n, uint8_t *__re
         const uint4 *s16 = reinterpret_cast<const uint4 *>(src + head);
         uint4 *d16 = reinterpret_cast<uint4 *>(dst + head);
         uint32_t k = threadIdx.x;
-        for (; k + 3 * blockDim.x < nvec; k += 4 * blockDim.x) {
-            const uint4 a = s16[k], b = s16[k + blockDim.x], c = s16[k + 2 * blockDim.x], e = s16[k + 3 * blockDim.x];
-            d16[k] = a;
-            d16[k + blockDim.x] = b;
-            d16[k + 2 * blockDim.x] = c;
-            d16[k + 3 * blockDim.x] = e;
+        for (; k + (kInFlight - 1) * blockDim.x < nvec; k += kInFlight * blockDim.x) {
+            uint4 v[kInFlight]; // all loads of a pass are issued before its stores
+#pragma unroll
+            for (int u = 0; u < kInFlight; u++) v[u] = s16[k + u * blockDim.x];
+#pragma unroll
+            for (int u = 0; u < kInFlight; u++) d16[k + u * blockDim.x] = v[u];
         }
         for (; k < nvec; k += blockDim.x) d16[k] = s16[k];
         for (uint32_t t = head + (nvec << 4) + threadIdx.x; t < size; t += blockDim.x) dst[t] = src[t];
     }
 }
 
-void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, int ctas, cudaStream_t stream) {
+void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, int ctas, int in_flight, cudaStream_t stream) {
     if (n <= 0) return;
     if (ctas < 1) ctas = kGatherCtas;
     const int grid = n < ctas ? n : ctas;
-    gather_payloads_kernel<<<grid, 256, 0, stream>>>(descs, n, blob);
+    if (in_flight >= 8)
+        gather_payloads_kernel<8><<<grid, 256, 0, stream>>>(descs, n, blob);
+    else
+        gather_payloads_kernel<4><<<grid, 256, 0, stream>>>(descs, n, blob);
 }
 
 } // namespace ffcvb

@@ -9,9 +9,10 @@ namespace ffcvb {
 
 // Pulls every sample's payload from pinned host memory (descs[i].src_addr, read by the SMs over
 // PCIe) into its place in the device blob.  Source and destination share their alignment mod 16.
-// `ctas`: CTAs of 256 threads that fetch (< 1: kGatherCtas).
+// `ctas`: CTAs of 256 threads that fetch (< 1: kGatherCtas); `in_flight`: 16-byte loads a thread
+// of a JPEG payload's copy has outstanding (4 or 8).
 constexpr int kGatherCtas = 16;
-void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, int ctas, cudaStream_t stream);
+void launch_gather_payloads(const ImageDesc *descs, int n, uint8_t *blob, int ctas, int in_flight, cudaStream_t stream);
 
 // Longest subsequence whose chunk the entropy decoder stages in shared memory.
 constexpr int kMaxStagedBits = 1280;
