@@ -86,6 +86,8 @@ def parse_args():
     ap.add_argument('--no-cpu-baseline', action='store_true', help='skip the CPU oracle leg (profiling runs)')
     ap.add_argument('--no-configs', action='store_true', help='skip the short pass over the other configurations')
     ap.add_argument('--no-modes', action='store_true', help='skip the other staging modes (e2e_staged, e2e_gather, ...)')
+    ap.add_argument('--decode-index', type=float, default=0.0,
+                    help='GiB of GPU memory for the decode index (Loader(decode_index_gb=...)); 0 = off, the default')
     ap.add_argument('--dct-downscale', action='store_true',
                     help='decode JPEG samples at reduced scale where the crop allows (not the reference\'s pixels)')
     ap.add_argument('--batch', type=int, default=0, help='profiling runs: batch size instead of the configuration\'s')
@@ -367,6 +369,7 @@ class Bench:
                 sys.stdout.flush()
                 os.dup2(saved, 1)
                 os.close(saved)
+        self.decode_index = args.decode_index
         self.cores = len(os.sched_getaffinity(0))
         self.workers = args.workers or max(2, self.cores // max(1, self.world))
 
@@ -395,7 +398,8 @@ class Bench:
         return Loader(path, batch_size=w['batch'], order=getattr(OrderOption, w['order']), distributed=self.world > 1,
                       seed=0, num_workers=self.workers,
                       pipelines=build_pipelines(cfg, self.device, self.args.dct_downscale),
-                      batches_ahead=self.args.batches_ahead, drop_last=True, pin_file=pin, cpu_stage_share=share, **kw)
+                      batches_ahead=self.args.batches_ahead, drop_last=True, pin_file=pin, cpu_stage_share=share,
+                      decode_index_gb=self.decode_index, **kw)
 
     @staticmethod
     def describe(ld):
@@ -507,6 +511,8 @@ class Bench:
         self.barrier()
         path = dataset_path(cfg, images, args.restart_interval)
         out = {'config': config_dict(cfg, self.world, images, self.workers, args.restart_interval)}
+        if self.decode_index > 0:
+            out['config']['decode_index_gb'] = self.decode_index  # opt-in: states recorded by a stream's first decode
         if args.dct_downscale:
             out['config']['dct_downscale'] = 'JPEG samples decoded at 1/2 .. 1/8 where the crop allows (opt-in: not the reference\'s pixels)'
 
@@ -579,6 +585,8 @@ class Bench:
         serial_ms = s0.elapsed_time(s1)
         ctx.set_profiling(False)
         out['infos'] = infos
+        if self.decode_index > 0:
+            out['decode_index_stats'] = ctx.decode_index_stats()
         if args.kernels_only:
             value_ms = serial_ms
         else:
@@ -720,6 +728,23 @@ class Bench:
                                         'kernel_ms': {n: r['kernels'][n]['ms'] for n in KERNELS}}
                 except Exception as exc:  # noqa: BLE001 - a side measurement must not take the headline down
                     configs[f'c{c}'] = {'error': f'{type(exc).__name__}: {exc}'}
+        # the same measurement with the decode index on (opt-in feature, reported beside the headline)
+        indexed = {}
+        if self.world == 1 and not args.no_configs and not args.kernels_only and self.decode_index == 0:
+            self.decode_index = 1.0
+            for c in sorted(WORKLOADS):
+                if c == 0:
+                    continue  # no JPEG samples
+                st = min(args.steps, 8 if c == 4 else 20)
+                try:
+                    r = self.measure(c, st, min(args.warmup, 3 if c == 4 else 5), full=False)
+                    indexed[f'c{c}'] = {'value': r['value'], 'ms_per_step': r['ms_per_step'], 'e2e': r['e2e']['value'],
+                                        'e2e_ms_per_step': r['e2e']['ms_per_step'],
+                                        'kernel_ms': {n: r['kernels'][n]['ms'] for n in KERNELS},
+                                        'index': r.get('decode_index_stats')}
+                except Exception as exc:  # noqa: BLE001
+                    indexed[f'c{c}'] = {'error': f'{type(exc).__name__}: {exc}'}
+            self.decode_index = 0.0
         if self.rank != 0:
             if self.world > 1:
                 self.dist.destroy_process_group()
@@ -771,6 +796,10 @@ class Bench:
                      'clocks': clocks})
         if configs:
             line['configs'] = configs
+        if indexed:
+            line['decode_index'] = {'note': 'Loader(decode_index_gb=1): every JPEG stream decoded once before leaves the decoder states '
+                                            'of its subsequences in GPU memory; later decodes take one pass from them (same pixels). '
+                                            'Opt-in; the headline figures above are measured without it.', **indexed}
         print(json.dumps(line, default=float))
         if self.world > 1:
             self.dist.destroy_process_group()

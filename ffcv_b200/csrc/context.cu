@@ -17,6 +17,7 @@
 #include <mutex>
 #include <string>
 #include <thread>
+#include <unordered_map>
 #include <chrono>
 #include <vector>
 
@@ -266,6 +267,19 @@ struct ffcvb_ctx {
     // FFCV_B200_GATHER_IN_FLIGHT.
     int tune_copy_threads = 0, tune_subseq_bits = 0, tune_entropy_threads = 0, gather_ctas = 0, gather_in_flight = 8;
     DevBuf one_src, one_dst; // single-image entry points
+    // Decode index (ffcvb_set_decode_index): a pool of device memory that keeps, per JPEG stream seen,
+    // the decoder states a finished decode left behind; entries are handed out in order and never
+    // moved.  Keyed by the sample's offset in the file: the context then serves one file.
+    struct IndexEntry {
+        uint64_t off;
+        uint32_t cap;
+        uint32_t subseq_bits;
+        uint64_t created_seq;
+    };
+    DevBuf index_pool, index_stats;
+    size_t index_used = 0;
+    std::unordered_map<uint64_t, IndexEntry> index_map;
+    uint64_t stage_seq = 0;
 };
 
 namespace {
@@ -420,6 +434,8 @@ void ffcvb_destroy(ffcvb_ctx *ctx) {
         if (a.host) cudaFreeHost(a.host);
         if (a.ev) cudaEventDestroy(a.ev);
     }
+    if (ctx->index_pool.p) cudaFree(ctx->index_pool.p);
+    if (ctx->index_stats.p) cudaFree(ctx->index_stats.p);
     if (ctx->one_src.p) cudaFree(ctx->one_src.p);
     if (ctx->one_dst.p) cudaFree(ctx->one_dst.p);
     delete ctx->pool;
@@ -806,6 +822,47 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
         }
     }
 
+    // ---- entropy decode configuration: CTA size and longest subsequence by the batch's largest
+    // scan; with a decode index every image gets a subsequence length of its own and its entry
+    pick_entropy_config(scan_bytes_par, &s.entropy_threads, &s.subseq_bits);
+    if (ctx->tune_subseq_bits) s.subseq_bits = ctx->tune_subseq_bits;
+    if (ctx->tune_entropy_threads) s.entropy_threads = ctx->tune_entropy_threads;
+    ctx->stage_seq++;
+    for (int i : par_list) {
+        ImageDesc &d = descs[i];
+        d.subseq_bits = (uint32_t)s.subseq_bits;
+        d.index_cap = 0;
+        d.index_off = 0;
+        if (!ctx->index_pool.p || d.host_status != 0) continue;
+        // a function of the stream alone (the CTA size its own length would get), so that the
+        // recorded states stay usable whatever batch the sample lands in next time
+        int own_threads, own_bits;
+        pick_entropy_config(d.scan_len, &own_threads, &own_bits);
+        const size_t own = (size_t)own_bits;
+        d.subseq_bits = (uint32_t)own;
+        const uint64_t key = ptrs[i];
+        auto it = ctx->index_map.find(key);
+        if (it != ctx->index_map.end() && it->second.subseq_bits != d.subseq_bits) {
+            // the batch's CTA size changed the subsequence length: the old entry is of no use
+            // (its memory stays with the pool); a new one is recorded
+            ctx->index_map.erase(it);
+            it = ctx->index_map.end();
+        }
+        if (it == ctx->index_map.end()) {
+            const uint32_t cap = (uint32_t)(((size_t)d.scan_len * 8 + own - 1) / own + 2);
+            const size_t bytes = decode_index_bytes(cap);
+            if (ctx->index_used + bytes > ctx->index_pool.cap) continue; // pool full: this stream stays unindexed
+            ffcvb_ctx::IndexEntry e{ctx->index_used, cap, d.subseq_bits, ctx->stage_seq};
+            ctx->index_used += bytes;
+            it = ctx->index_map.emplace(key, e).first;
+        } else if (ctx->stage_seq - it->second.created_seq < ctx->slots.size()) {
+            // recorded by a batch that may still be running on another slot's stream: hands off
+            continue;
+        }
+        d.index_off = it->second.off;
+        d.index_cap = it->second.cap;
+    }
+
     BatchHeader &hd = s.hdr;
     memset(&hd, 0, sizeof(hd));
     hd.n = (uint32_t)n;
@@ -1004,9 +1061,6 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     s.clean_bytes = clean_bytes;
     s.plane_bytes = plane_bytes;
     s.rgb_bytes = rgb_bytes;
-    pick_entropy_config(scan_bytes_par, &s.entropy_threads, &s.subseq_bits);
-    if (ctx->tune_subseq_bits) s.subseq_bits = ctx->tune_subseq_bits;
-    if (ctx->tune_entropy_threads) s.entropy_threads = ctx->tune_entropy_threads;
     {
         const size_t need = entropy_checkpoint_bytes((int)par_list.size(), s.entropy_threads, s.subseq_bits);
         if (need && (rc = grow_dev(ctx, s.ckpt, need))) return rc;
@@ -1124,7 +1178,8 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         const int32_t *sl = reinterpret_cast<const int32_t *>(blob + s.seq_list_off);
         launch_entropy_decode(descs, pl, s.n_par, sl, s.n_seq, blob, huff, (uint8_t *)s.clean.p,
                               (int16_t *)s.coef.p, status, s.subseq_bits, s.entropy_threads,
-                              s.subseq_bits > kMaxStagedBits ? s.ckpt.p : nullptr, st);
+                              s.subseq_bits > kMaxStagedBits ? s.ckpt.p : nullptr, (uint8_t *)ctx->index_pool.p,
+                              (unsigned long long *)ctx->index_stats.p, st);
         if (prof) CU(cudaEventRecord(s.ev[2], st));
         launch_idct(descs, jl, s.n_jpeg, s.total_blocks, mult, (const int16_t *)s.coef.p,
                     (uint8_t *)s.planes.p, st);
@@ -1174,6 +1229,41 @@ int ffcvb_set_batch_riders(ffcvb_ctx *ctx, int slot, const ffcvb_rider *riders, 
         }
         s.pending_riders.push_back(std::move(r));
     }
+    return FFCVB_OK;
+}
+
+int ffcvb_set_decode_index(ffcvb_ctx *ctx, uint64_t bytes) {
+    if (!ctx) return FFCVB_E_ARG;
+    ctx->pool->wait_all();
+    CU(cudaSetDevice(ctx->device));
+    CU(cudaDeviceSynchronize());
+    if (ctx->index_pool.p) {
+        CU(cudaFree(ctx->index_pool.p));
+        ctx->index_pool = DevBuf{};
+    }
+    ctx->index_map.clear();
+    ctx->index_used = 0;
+    if (bytes == 0) return FFCVB_OK;
+    bytes = align_up((size_t)bytes, 1 << 20);
+    CU(cudaMalloc(&ctx->index_pool.p, (size_t)bytes));
+    ctx->index_pool.cap = (size_t)bytes;
+    CU(cudaMemset(ctx->index_pool.p, 0, (size_t)bytes)); // no entry is valid yet
+    if (!ctx->index_stats.p) {
+        CU(cudaMalloc(&ctx->index_stats.p, 64));
+        ctx->index_stats.cap = 64;
+    }
+    CU(cudaMemset(ctx->index_stats.p, 0, 64));
+    return FFCVB_OK;
+}
+
+int ffcvb_decode_index_stats(ffcvb_ctx *ctx, uint64_t *out) {
+    if (!ctx || !out) return FFCVB_E_ARG;
+    out[0] = out[1] = 0;
+    out[2] = ctx->index_map.size();
+    out[3] = ctx->index_used;
+    if (!ctx->index_stats.p) return FFCVB_OK;
+    CU(cudaSetDevice(ctx->device));
+    CU(cudaMemcpy(out, ctx->index_stats.p, 16, cudaMemcpyDeviceToHost));
     return FFCVB_OK;
 }
 

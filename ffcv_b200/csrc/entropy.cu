@@ -252,11 +252,15 @@ __device__ __forceinline__ int count_span_checked(const uint32_t *__restrict__ w
 // re-synchronise in two or three (long, fully parallel) rounds instead of dozens of chunks that
 // wait for one another.
 template <int kEntropyThreads, bool kStaged>
-__global__ void __launch_bounds__(kEntropyThreads, 1536 / kEntropyThreads)
+// (resident CTAs per SM: shared memory -- 27 KB of tables plus the stream -- allows 2 CTAs of 512
+// threads, 3 of 256 and 4 of 128 in the staged variants, so the register budget is set for those
+// counts rather than for full thread occupancy)
+__global__ void __launch_bounds__(kEntropyThreads, kEntropyThreads >= 1024 ? 1 : (kEntropyThreads == 512 ? 2 : (kEntropyThreads == 256 ? 4 : 6)))
 entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
                         const uint8_t *__restrict__ blob, const HuffTable *__restrict__ huff,
                         uint8_t *__restrict__ clean, int16_t *__restrict__ coef,
-                        int32_t *__restrict__ status, int subseq_bits, CheckPoint *__restrict__ ckpt, int ck_bits) {
+                        int32_t *__restrict__ status, int subseq_bits, CheckPoint *__restrict__ ckpt, int ck_bits,
+                        uint8_t *__restrict__ index_pool, unsigned long long *__restrict__ index_stats) {
     extern __shared__ __align__(16) uint32_t s_stream[]; // this chunk of the unstuffed stream
     __shared__ HuffTable s_tab[6];
     __shared__ unsigned long long s_state[kEntropyThreads + 1];
@@ -265,6 +269,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
     __shared__ uint8_t s_dirty[kEntropyThreads + 1];
     __shared__ int s_warp[33];
     __shared__ uint8_t s_zz[64];
+    __shared__ uint32_t s_ix[2]; // decisions about the decode index, taken by one thread for the whole CTA
 
     const int img = list[blockIdx.x];
     const ImageDesc d = descs[img];
@@ -332,10 +337,56 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
 
     const uint32_t *words = reinterpret_cast<const uint32_t *>(cl);
     const uint32_t total_bits = clean_len * 8;
-    const uint32_t S = (uint32_t)subseq_bits;
+    // this image's subsequence length; `subseq_bits` is the batch's longest, which sized the buffers
+    const uint32_t S = d.subseq_bits ? d.subseq_bits : (uint32_t)subseq_bits;
     const int bpm = d.bpm, luma = d.hs * d.vs, ncomp = d.ncomp;
     int16_t *cf = coef + (size_t)d.block_base * 64;
 
+    // ---- decode index: the states a finished decode of this very stream left behind
+    DecodeIndexHeader *ix_hdr = nullptr;
+    unsigned long long *ix_state = nullptr;
+    uint32_t *ix_blocks = nullptr;
+    bool indexed = false;
+    if (index_pool != nullptr && d.index_cap != 0) {
+        ix_hdr = reinterpret_cast<DecodeIndexHeader *>(index_pool + d.index_off);
+        ix_state = reinterpret_cast<unsigned long long *>(ix_hdr + 1);
+        ix_blocks = reinterpret_cast<uint32_t *>(ix_state + d.index_cap + 1);
+        if (tid == 0) {
+            const volatile DecodeIndexHeader *h = ix_hdr; // entries are written by other launches: no caching
+            const uint32_t v = h->valid_subs;
+            const bool ok = h->magic == kDecodeIndexMagic && h->scan_len == d.scan_len && h->subseq_bits == S &&
+                            h->clean_len == clean_len && v <= d.index_cap && __ldcg(ix_blocks + v) >= d.nblocks;
+            s_ix[0] = ok ? 1u : 0u;
+            s_ix[1] = v;
+        }
+        __syncthreads();
+        indexed = s_ix[0] != 0;
+        const uint32_t valid = s_ix[1];
+        if (indexed) {
+            // Every subsequence starts from its recorded state and writes straight to its recorded
+            // place: one pass, no guessing.  (Uniform branch: all threads read the same header.)
+            {
+                uint4 *z16 = reinterpret_cast<uint4 *>(cf);
+                for (uint32_t k = tid; k < d.nblocks * 8; k += kEntropyThreads) z16[k] = make_uint4(0, 0, 0, 0);
+            }
+            __syncthreads();
+            for (uint32_t t = tid; t < valid; t += kEntropyThreads) {
+                const uint32_t b0 = __ldcg(ix_blocks + t);
+                if (b0 >= d.nblocks) break; // the crop needs nothing from here on
+                Cursor cur = unpack(__ldcg(ix_state + t));
+                uint32_t t_end = (t + 1) * S;
+                if (t_end > total_bits) t_end = total_bits;
+                decode_span<true>(words, 0, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, cf, b0, d.nblocks);
+            }
+            if (tid == 0) {
+                status[img] = 0;
+                if (index_stats) atomicAdd(index_stats, 1ull);
+            }
+            __syncthreads();
+        }
+    }
+
+    if (!indexed) {
     Cursor zero = {0, 0, 0};
     unsigned long long carry = pack(zero);
     uint32_t blk_base = 0, zeroed_to = 0;
@@ -411,7 +462,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
                 bool merged = false;
                 if (!kStaged && ckpt != nullptr) {
                     // long subsequences: stop where this walk rejoins the previous one
-                    const uint32_t per_sub = S / (uint32_t)ck_bits + 1;
+                    const uint32_t per_sub = (uint32_t)subseq_bits / (uint32_t)ck_bits + 1; // stride: the batch's longest
                     CheckPoint *ck = ckpt + ((size_t)blockIdx.x * kEntropyThreads + (size_t)t) * per_sub;
                     int total;
                     if (iter == 0)
@@ -437,6 +488,39 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         const int my_blocks = active ? s_blocks[tid] : 0;
         int chunk_blocks;
         const int first = block_scan_exclusive(my_blocks, s_warp, chunk_blocks);
+        if (ix_hdr != nullptr && chunk == 0 && first_sub == 0 && (uint32_t)nsub <= d.index_cap) {
+            // the entry states are final now: leave them, and the blocks before each, for the next
+            // decode of this stream (unless an entry that reaches at least as far is there already)
+            if (tid == 0) {
+                const volatile DecodeIndexHeader *h = ix_hdr;
+                const bool keep = h->magic == kDecodeIndexMagic && h->scan_len == d.scan_len && h->subseq_bits == S &&
+                                  h->clean_len == clean_len && h->valid_subs >= (uint32_t)nsub;
+                s_ix[0] = keep ? 1u : 0u;
+                if (!keep) ix_hdr->magic = 0;
+            }
+            __syncthreads();
+            if (s_ix[0] == 0) {
+                if (active) {
+                    ix_state[tid] = s_state[tid];
+                    ix_blocks[tid] = (uint32_t)first;
+                }
+                if (tid == 0) {
+                    ix_state[nsub] = s_state[nsub];
+                    ix_blocks[nsub] = (uint32_t)chunk_blocks;
+                }
+                __threadfence();
+                __syncthreads();
+                if (tid == 0) {
+                    ix_hdr->scan_len = d.scan_len;
+                    ix_hdr->subseq_bits = S;
+                    ix_hdr->clean_len = clean_len;
+                    ix_hdr->valid_subs = (uint32_t)nsub;
+                    __threadfence();
+                    ix_hdr->magic = kDecodeIndexMagic;
+                    if (index_stats) atomicAdd(index_stats + 1, 1ull);
+                }
+            }
+        }
         // Only non-zero coefficients are stored, so the blocks this chunk writes to are cleared
         // first: the ones it completes and the one left in progress at its end.  Done here rather
         // than by a device-wide memset long before, the cleared lines are still in L2 when the
@@ -468,6 +552,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         for (uint32_t k = tid; k < nvec; k += kEntropyThreads) z16[k] = make_uint4(0, 0, 0, 0);
     }
     __syncthreads();
+    } // !indexed
 
     // ---- integrate the DC differences of each component over the scan
     const int nmcu = d.mcus_x * d.mcu_rows; // the MCUs that were decoded
@@ -658,14 +743,16 @@ entropy_restart_kernel(const ImageDesc *__restrict__ descs, const int32_t *__res
 void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
                            const int32_t *seq_list, int n_seq, const uint8_t *blob,
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
-                           int subseq_bits, int entropy_threads, void *checkpoints, cudaStream_t stream) {
+                           int subseq_bits, int entropy_threads, void *checkpoints, uint8_t *index_pool,
+                           unsigned long long *index_stats, cudaStream_t stream) {
     if (n_list > 0) {
         const bool staged = subseq_bits <= kMaxStagedBits;
         auto launch = [&](auto kernel, int threads) {
             const size_t smem = staged ? ((size_t)threads * subseq_bits / 8 + 63) / 16 * 16 + 16 : 16;
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             kernel<<<n_list, threads, smem, stream>>>(descs, list, blob, huff, clean, coef, status, subseq_bits,
-                                                      static_cast<CheckPoint *>(checkpoints), kCheckPointBits);
+                                                      static_cast<CheckPoint *>(checkpoints), kCheckPointBits,
+                                                      index_pool, index_stats);
         };
         switch (entropy_threads) {
         case 128:

@@ -35,10 +35,15 @@ inline size_t entropy_checkpoint_bytes(int n_images, int entropy_threads, int su
 // every block they decode into.  `checkpoints`: entropy_checkpoint_bytes(n_list, ...) bytes of device
 // scratch when the subsequences are longer than kMaxStagedBits (may be nullptr: then every repair
 // pass walks its whole subsequence).
+// `subseq_bits` is the longest subsequence of the batch (an image's own length is
+// descs[i].subseq_bits <= subseq_bits).  `index_pool` / `index_stats`: the decode index (see
+// DecodeIndexHeader; descs[i].index_off / index_cap place an image's entry) and two counters
+// (images decoded from their index entry, entries written); both may be nullptr.
 void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_list,
                            const int32_t *seq_list, int n_seq, const uint8_t *blob,
                            const HuffTable *huff, uint8_t *clean, int16_t *coef, int32_t *status,
-                           int subseq_bits, int entropy_threads, void *checkpoints, cudaStream_t stream);
+                           int subseq_bits, int entropy_threads, void *checkpoints, uint8_t *index_pool,
+                           unsigned long long *index_stats, cudaStream_t stream);
 
 // Dequantise + fast integer IDCT of `total_blocks` blocks into the 8-bit component planes.
 void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32_t total_blocks,

@@ -146,7 +146,7 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     subseq = subseq < 512 ? 512 : (subseq > 1280 ? 1280 : subseq);
     launch_entropy_decode(desc_dev, list_dev, sequential ? 0 : 1, list_dev, sequential ? 1 : 0, jpeg_dev, meta_dev->huff,
                           scratch + kCleanOff, reinterpret_cast<int16_t *>(scratch + kCoefOff), meta_dev->status,
-                          (int)subseq, 512, nullptr, st);
+                          (int)subseq, 512, nullptr, nullptr, nullptr, st);
     launch_idct(desc_dev, list_dev, 1, d.nblocks, meta_dev->mult, reinterpret_cast<const int16_t *>(scratch + kCoefOff),
                 scratch + kPlaneOff, st);
     const bool quad = d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (width + 1) / 2 >= 3;

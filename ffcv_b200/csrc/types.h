@@ -37,6 +37,11 @@ struct ImageDesc {
     // image have the same resolution.  dec_* equal height / width for unscaled and raw samples.
     uint8_t scale_shift, bs_luma, bs_chroma;
     uint16_t dec_height, dec_width;
+    // Speculative entropy decode: length in bits of this image's subsequences (multiple of 128), and
+    // its place in the decode index (index_cap == 0: none), see DecodeIndexHeader.
+    uint32_t subseq_bits;
+    uint32_t index_cap;    // subsequences the index entry has room for
+    uint64_t index_off;    // byte offset of the entry in the context's index pool
     // The crop box decides how much of the image is needed: the entropy decoder stops after
     // `mcu_rows` rows of MCUs and the inverse transform runs only on the MCUs of the box below
     // (the crop box grown by the reach of the chroma filter).  Whole image when there is no crop.
@@ -88,6 +93,25 @@ struct MultTable {
     int16_t m[64];
     uint16_t q[64];
 };
+
+// Decode index: what a finished speculative decode of a stream knows and the next decode of the
+// same stream can start from -- the exact decoder state at the start of every subsequence and the
+// number of blocks completed before it.  With it every subsequence is decoded once, straight into
+// its final place: no guessing, no repair rounds.  An entry lives in device memory:
+//   [DecodeIndexHeader][uint64 state x (cap + 1)][uint32 blocks_before x (cap + 1)]
+// and is valid when `magic` is set (written last) and scan_len / subseq_bits / clean_len match.
+struct DecodeIndexHeader {
+    uint32_t magic, scan_len, subseq_bits, valid_subs; // entries 0 .. valid_subs are final
+    uint32_t clean_len, reserved[3];
+};
+constexpr uint32_t kDecodeIndexMagic = 0x58444946u;
+inline
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+size_t decode_index_bytes(uint32_t cap) {
+    return (sizeof(DecodeIndexHeader) + (size_t)(cap + 1) * 12 + 15) / 16 * 16;
+}
 
 struct BatchHeader {
     uint32_t n, n_huff, n_mult, n_params; // n_params = int32 per sample

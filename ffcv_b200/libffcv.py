@@ -61,6 +61,10 @@ lib.ffcvb_submit_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_submit_batch.restype = c_int
 lib.ffcvb_rerun_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_rerun_batch.restype = c_int
+lib.ffcvb_set_decode_index.argtypes = [c_void_p, c_uint64]
+lib.ffcvb_set_decode_index.restype = c_int
+lib.ffcvb_decode_index_stats.argtypes = [c_void_p, c_void_p]
+lib.ffcvb_decode_index_stats.restype = c_int
 lib.ffcvb_set_async_staging.argtypes = [c_void_p, c_int]
 lib.ffcvb_set_async_staging.restype = c_int
 lib.ffcvb_color_jitter.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
@@ -243,6 +247,15 @@ class Context:
 
     def staging_split(self):
         return int(lib.ffcvb_staging_split(self._h))
+
+    def set_decode_index(self, nbytes):
+        """Device memory for the decode index (0: off); see ffcvb_set_decode_index."""
+        self._check(lib.ffcvb_set_decode_index(self._h, int(nbytes)), 'ffcvb_set_decode_index')
+
+    def decode_index_stats(self):
+        out = np.zeros(4, dtype=np.uint64)
+        self._check(lib.ffcvb_decode_index_stats(self._h, out.ctypes.data), 'ffcvb_decode_index_stats')
+        return dict(zip(('used', 'recorded', 'entries', 'bytes'), (int(v) for v in out)))
 
     def set_async_staging(self, enabled):
         self._check(lib.ffcvb_set_async_staging(self._h, int(bool(enabled))), 'ffcvb_set_async_staging')

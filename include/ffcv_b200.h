@@ -150,6 +150,20 @@ typedef struct {
 } ffcvb_rider;
 int ffcvb_set_batch_riders(ffcvb_ctx *ctx, int slot, const ffcvb_rider *riders, int n_riders, int n);
 
+/* Decode index (no counterpart in the reference).  A loader decodes the same JPEG streams epoch
+ * after epoch, and what makes the decode of a stream without restart markers expensive on a GPU
+ * -- finding the decoder's state at the start of every subsequence -- is the same every time.
+ * With an index of `bytes` bytes of device memory (0 switches it off and frees it) the first decode
+ * of a stream records those states (12 bytes per subsequence of 0.5-1.3 kbit: about 7 % of the
+ * stream's size) and later decodes of the same stream start every subsequence from its recorded
+ * state: one pass instead of the guess-and-repair rounds, same pixels.  Streams are told apart by
+ * their offset in the file, so a context with an index must serve one file; entries of streams
+ * recorded while the pool was full are simply never made.  ffcvb_decode_index_stats: out[0]
+ * images decoded from their entry, out[1] entries recorded, out[2] entries in the table, out[3]
+ * bytes of the pool in use. */
+int ffcvb_set_decode_index(ffcvb_ctx *ctx, uint64_t bytes);
+int ffcvb_decode_index_stats(ffcvb_ctx *ctx, uint64_t *out);
+
 /* With asynchronous staging enabled, ffcvb_stage_batch returns as soon as the batch is laid out
  * and leaves the payload copy running on the staging threads.  ffcvb_submit_batch of that slot
  * does not wait for it either: it queues a stream callback that holds `stream` until the copy is

@@ -468,3 +468,29 @@ def test_dct_domain_downscale_option(datasets, cfg, res, batch):
     b = next(iter(_loader(datasets[cfg], batch, plain, order=OrderOption.QUASI_RANDOM)))[0]
     assert a.shape == b.shape and not ch.equal(a, b)
     assert (a.float() - b.float()).abs().mean() < 0.1  # same picture, different rounding path
+
+
+@pytest.mark.parametrize('cfg,res,batch,epochs', [(2, 224, 32, 3), (1, 160, 64, 3), (4, 384, 3, 3)])
+def test_decode_index_gives_the_same_pixels(datasets, cfg, res, batch, epochs):
+    """`Loader(decode_index_gb=...)`: the first decode of a JPEG sample records the decoder states at
+    the start of its subsequences, later epochs decode it in one pass from them.  Every epoch must
+    still equal the oracle bit for bit (crops differ from epoch to epoch, so entries recorded for a
+    small crop get extended by larger ones), and the index must actually be used."""
+    from ffcv_b200 import OrderOption
+    from ffcv_b200.fields.decoders import RandomResizedCropRGBImageDecoder
+    from ffcv_b200.transforms import NormalizeImage, RandomHorizontalFlip, ToTorchImage
+    pipes = {'image': [RandomResizedCropRGBImageDecoder((res, res)), RandomHorizontalFlip(),
+                       NormalizeImage(IMAGENET_MEAN, IMAGENET_STD, np.float16), ToTorchImage()],
+             'label': None}
+    loader = _loader(datasets[cfg], batch, pipes, order=OrderOption.RANDOM, decode_index_gb=0.05, batches_ahead=1)
+    ctx = image_executor(loader).ctx
+    seen = []
+    for _ in range(epochs):
+        compare_epoch(loader)
+        ch.cuda.synchronize()
+        seen.append(ctx.decode_index_stats())
+    n_jpeg = int((loader.reader.metadata['f0']['mode'] == 0).sum())
+    assert seen[0]['recorded'] >= 1 and seen[-1]['entries'] >= min(n_jpeg, 1)
+    assert seen[-1]['used'] > seen[0]['used'] and seen[-1]['used'] >= n_jpeg // 2, seen
+    status = ctx.status(0, ch.cuda.current_stream().cuda_stream, 1)
+    assert (status == 0).all()
