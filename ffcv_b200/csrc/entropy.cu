@@ -17,11 +17,6 @@
 namespace ffcvb {
 
 
-__device__ __constant__ uint8_t kZigzagNatural[64] = {
-    0,  1,  8,  16, 9,  2,  3,  10, 17, 24, 32, 25, 18, 11, 4,  5,  12, 19, 26, 33, 40, 48,
-    41, 34, 27, 20, 13, 6,  7,  14, 21, 28, 35, 42, 49, 56, 57, 50, 43, 36, 29, 22, 15, 23,
-    30, 37, 44, 51, 58, 59, 52, 45, 38, 31, 39, 46, 53, 60, 61, 54, 47, 55, 62, 63};
-
 // Exclusive prefix sum over the block; `total` receives the block sum.  s_warp holds 33 ints.
 __device__ __forceinline__ int block_scan_exclusive(int v, int *s_warp, int &total) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -140,7 +135,7 @@ __device__ __forceinline__ Cursor unpack(uint64_t v) {
 template <bool WRITE>
 __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, uint32_t bit_base, Cursor &cur,
                                            uint32_t end, int bpm, int luma, int ncomp,
-                                           const HuffTable *s_tab, const uint8_t *s_zz,
+                                           const HuffTable *s_tab,
                                            int16_t *__restrict__ cf, uint32_t blk,
                                            uint32_t nblocks) {
     int done = 0;
@@ -149,6 +144,16 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
     int comp2 = (ncomp == 1 || c < luma) ? 0 : 2 * (c - luma + 1);
     int16_t *out = cf + (size_t)blk * 64;
     if (p >= end) return 0;
+    // Coefficients are stored in the order they are decoded (zig-zag order inside a block; the
+    // inverse transform undoes it when it loads the block), which lets a thread collect the four
+    // coefficients of an aligned group of zig-zag positions in a register and store them with one
+    // 8-byte store: a block's ~15 non-zero coefficients sit in ~5 such groups, and scattered stores
+    // are what the write pass is bound by.  Only a block this thread decodes from its first symbol
+    // is packed: a block shared with a neighbouring subsequence is written coefficient by
+    // coefficient, so that the two threads never touch the same bytes.
+    bool packing = z == 0;
+    int group = -1; // group of four positions held in `held`, -1: none
+    unsigned long long held = 0;
     BitWindow win(words, p - bit_base);
     while (p < end) {
         const uint32_t w = win.peek();
@@ -160,8 +165,20 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
         if (WRITE) {
             // where this symbol's coefficient goes, if it has one
             const int zpos = zn - 1;
-            if (s != 0 && zpos < 64 && blk < nblocks)
-                out[dc ? 0 : s_zz[zpos]] = (int16_t)extend((w << (n - s)) >> (32 - s), s);
+            if (s != 0 && zpos < 64 && blk < nblocks) {
+                const int v = extend((w << (n - s)) >> (32 - s), s);
+                if (packing) {
+                    const int g = zpos >> 2;
+                    if (g != group) {
+                        if (group >= 0) *reinterpret_cast<unsigned long long *>(out + 4 * group) = held;
+                        group = g;
+                        held = 0;
+                    }
+                    held |= (unsigned long long)(uint16_t)v << (16 * (zpos & 3));
+                } else {
+                    out[zpos] = (int16_t)v;
+                }
+            }
         }
         p += n;
         win.skip(n);
@@ -169,11 +186,25 @@ __device__ __forceinline__ int decode_span(const uint32_t *__restrict__ words, u
         z = eob ? 0 : zn;
         done += eob ? 1 : 0;
         if (WRITE) {
+            if (eob) {
+                if (group >= 0) *reinterpret_cast<unsigned long long *>(out + 4 * group) = held;
+                group = -1;
+                packing = true;
+            }
             blk += eob ? 1 : 0;
             out += eob ? 64 : 0;
         }
         c = eob ? ((c + 1 == bpm) ? 0 : c + 1) : c;
         comp2 = (ncomp == 1 || c < luma) ? 0 : 2 * (c - luma + 1);
+    }
+    if (WRITE && group >= 0) {
+        // the subsequence ends inside a block: the next thread continues it, so only the
+        // coefficients themselves are written
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t lane = (uint32_t)(held >> (16 * k)) & 0xffffu;
+            if (lane) out[4 * group + k] = (int16_t)lane;
+        }
     }
     cur.p = p;
     cur.c = c;
@@ -268,7 +299,6 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
     __shared__ uint16_t s_list[kEntropyThreads];   // compacted indices of the dirty subsequences
     __shared__ uint8_t s_dirty[kEntropyThreads + 1];
     __shared__ int s_warp[33];
-    __shared__ uint8_t s_zz[64];
     __shared__ uint32_t s_ix[2]; // decisions about the decode index, taken by one thread for the whole CTA
 
     const int img = list[blockIdx.x];
@@ -289,7 +319,6 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
             da[i] = sa[i];
         }
     }
-    if (tid < 64) s_zz[tid] = kZigzagNatural[tid];
 
     // ---- remove byte stuffing (FF 00 -> FF) into the clean stream.  When the whole scan fits the
     // shared-memory stream buffer (the usual case: the subsequence length is chosen so that the
@@ -376,7 +405,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
                 Cursor cur = unpack(__ldcg(ix_state + t));
                 uint32_t t_end = (t + 1) * S;
                 if (t_end > total_bits) t_end = total_bits;
-                decode_span<true>(words, 0, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, cf, b0, d.nblocks);
+                decode_span<true>(words, 0, cur, t_end, bpm, luma, ncomp, s_tab, cf, b0, d.nblocks);
             }
             if (tid == 0) {
                 status[img] = 0;
@@ -473,7 +502,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
                                                          (uint32_t)ck_bits, merged);
                     s_blocks[t] = (uint16_t)total;
                 } else {
-                    s_blocks[t] = (uint16_t)decode_span<false>(stream, 0, cur, t_end, bpm, luma, ncomp, s_tab, s_zz, nullptr, 0, 0);
+                    s_blocks[t] = (uint16_t)decode_span<false>(stream, 0, cur, t_end, bpm, luma, ncomp, s_tab, nullptr, 0, 0);
                 }
                 if (!merged) {
                     const unsigned long long out = pack(cur);
@@ -538,7 +567,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         }
         if (active) {
             Cursor cur = unpack(s_state[tid]);
-            decode_span<true>(stream, 0, cur, sub_end, bpm, luma, ncomp, s_tab, s_zz, cf,
+            decode_span<true>(stream, 0, cur, sub_end, bpm, luma, ncomp, s_tab, cf,
                               blk_base + (uint32_t)first, d.nblocks);
         }
         carry = s_state[nsub];
@@ -600,7 +629,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
 // Returns the bit position reached, or 0xFFFFFFFF when the interval's bits ran out first.
 __device__ __forceinline__ uint32_t decode_interval(const uint32_t *__restrict__ words, uint32_t p, uint32_t limit,
                                                     uint32_t nblk, int bpm, int luma, int ncomp,
-                                                    const HuffTable *s_tab, const uint8_t *s_zz,
+                                                    const HuffTable *s_tab,
                                                     int16_t *__restrict__ cf, uint32_t blk) {
     int pred[3] = {0, 0, 0};
     int c = 0, z = 0;
@@ -622,7 +651,7 @@ __device__ __forceinline__ uint32_t decode_interval(const uint32_t *__restrict__
             pred[comp] += v;
             out[0] = (int16_t)pred[comp];
         } else if (s != 0 && zpos < 64) {
-            out[s_zz[zpos]] = (int16_t)v;
+            out[zpos] = (int16_t)v; // zig-zag order, as everywhere
         }
         p += n;
         win.skip(n);
@@ -645,7 +674,6 @@ entropy_restart_kernel(const ImageDesc *__restrict__ descs, const int32_t *__res
                        uint8_t *__restrict__ clean, int16_t *__restrict__ coef, int32_t *__restrict__ status) {
     __shared__ HuffTable s_tab[6];
     __shared__ int s_warp[33];
-    __shared__ uint8_t s_zz[64];
     __shared__ int s_bad;
 
     const int img = list[blockIdx.x];
@@ -665,7 +693,6 @@ entropy_restart_kernel(const ImageDesc *__restrict__ descs, const int32_t *__res
             da[i] = sa[i];
         }
     }
-    if (tid < 64) s_zz[tid] = kZigzagNatural[tid];
     if (tid == 0) s_bad = 0;
 
     // ---- remove byte stuffing and restart markers; note where every interval starts
@@ -732,7 +759,7 @@ entropy_restart_kernel(const ImageDesc *__restrict__ descs, const int32_t *__res
         const int count = nmcu - first < ri ? nmcu - first : ri;
         const uint32_t p0 = starts[k] * 8;
         const uint32_t limit = (k + 1 < found ? starts[k + 1] : clean_len) * 8;
-        const uint32_t p = decode_interval(words, p0, limit, (uint32_t)count * bpm, bpm, luma, ncomp, s_tab, s_zz, cf,
+        const uint32_t p = decode_interval(words, p0, limit, (uint32_t)count * bpm, bpm, luma, ncomp, s_tab, cf,
                                            (uint32_t)first * bpm);
         if (p == 0xFFFFFFFFu) s_bad = 1;
     }

@@ -12,6 +12,31 @@
 
 namespace ffcvb {
 
+// The entropy decoder leaves a block's coefficients in zig-zag order (the order it decodes them
+// in); position in that order of the coefficient of row r, column c: kZigzagOf[r * 8 + c].  Used
+// with compile-time indices only (fully unrolled loops), so the permutation costs nothing.
+__device__ __forceinline__ constexpr int zigzag_of(int n) {
+    constexpr int t[64] = {0, 1, 5, 6, 14, 15, 27, 28, 2, 4, 7, 13, 16, 26, 29, 42, 3, 8, 12, 17, 25, 30, 41, 43, 9, 11, 18, 24, 31, 40, 44, 53, 10, 19, 23, 32, 39, 45, 52, 54, 20, 22, 33, 38, 46, 51, 55, 60, 21, 34, 37, 47, 50, 56, 59, 61, 35, 36, 48, 49, 57, 58, 62, 63};
+    return t[n];
+}
+
+// Loads a block (64 int16 in zig-zag order, 16-byte aligned) into 32 registers of two.
+__device__ __forceinline__ void load_block(const int16_t *__restrict__ coef, int (&w)[32]) {
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        const int4 v = reinterpret_cast<const int4 *>(coef)[r];
+        w[4 * r] = v.x;
+        w[4 * r + 1] = v.y;
+        w[4 * r + 2] = v.z;
+        w[4 * r + 3] = v.w;
+    }
+}
+// Coefficient of natural position n (row-major) out of the registers load_block filled.
+__device__ __forceinline__ int coef_at(const int (&w)[32], int n) {
+    const int z = zigzag_of(n);
+    return (z & 1) ? (w[z >> 1] >> 16) : (int)(short)(w[z >> 1] & 0xffff);
+}
+
 __device__ __forceinline__ int w16(int v) { return (int)(short)v; }
 __device__ __forceinline__ int mul8(int v, int c) { return w16((v * c) >> 8); }
 
@@ -62,17 +87,16 @@ template <int R>
 __device__ __forceinline__ void reduced_block(const int16_t *__restrict__ coef, const uint16_t *__restrict__ q,
                                               uint8_t *__restrict__ dst, int pitch) {
     constexpr int N = 8 / R, L = R == 2 ? 1 : 2;
-    int a[8][8];
+    int a[8][8], cw[32];
+    load_block(coef, cw);
 #pragma unroll
     for (int r = 0; r < 8; r++) {
-        const int4 cw = reinterpret_cast<const int4 *>(coef)[r];
         const int4 qw = reinterpret_cast<const int4 *>(q)[r];
-        const int cc[4] = {cw.x, cw.y, cw.z, cw.w};
         const int qq[4] = {qw.x, qw.y, qw.z, qw.w};
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            a[r][2 * k] = (int)(short)(cc[k] & 0xffff) * (qq[k] & 0xffff);
-            a[r][2 * k + 1] = (cc[k] >> 16) * (int)((uint32_t)qq[k] >> 16);
+            a[r][2 * k] = coef_at(cw, r * 8 + 2 * k) * (qq[k] & 0xffff);
+            a[r][2 * k + 1] = coef_at(cw, r * 8 + 2 * k + 1) * (int)((uint32_t)qq[k] >> 16);
         }
     }
     int ws[8][N]; // [column of the block][row of the result]
@@ -162,18 +186,16 @@ idct_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ lis
         return;
     }
     const int16_t *q = mult[d.q_tab[comp]].m;
-    const int4 *src = reinterpret_cast<const int4 *>(coef + (size_t)gb * 64);
-    int v[8][8];
+    int v[8][8], cw[32];
+    load_block(coef + (size_t)gb * 64, cw);
 #pragma unroll
     for (int r = 0; r < 8; r++) {
-        const int4 cw = src[r];
         const int4 qw = reinterpret_cast<const int4 *>(q)[r];
-        const int cc[4] = {cw.x, cw.y, cw.z, cw.w};
         const int qq[4] = {qw.x, qw.y, qw.z, qw.w};
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            v[r][2 * k] = w16((int)(short)(cc[k] & 0xffff) * (int)(short)(qq[k] & 0xffff));
-            v[r][2 * k + 1] = w16((cc[k] >> 16) * (qq[k] >> 16));
+            v[r][2 * k] = w16(coef_at(cw, r * 8 + 2 * k) * (int)(short)(qq[k] & 0xffff));
+            v[r][2 * k + 1] = w16(coef_at(cw, r * 8 + 2 * k + 1) * (qq[k] >> 16));
         }
     }
 #pragma unroll

@@ -25,7 +25,7 @@ inline size_t entropy_checkpoint_bytes(int n_images, int entropy_threads, int su
 }
 
 // Entropy decode of every JPEG sample listed in `list` (indices into descs): unstuffs the scan
-// into `clean`, Huffman-decodes it into quantised coefficients (natural order inside a block,
+// into `clean`, Huffman-decodes it into quantised coefficients (zig-zag order inside a block,
 // blocks in scan order, DC un-differenced) in `coef`, and records a per-sample status.
 // `subseq_bits` is the length of the subsequences decoded speculatively in parallel (multiple
 // of 32), `entropy_threads` (128, 256, 512 or 1024) the CTA size: one CTA decodes one image,
