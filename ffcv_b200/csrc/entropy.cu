@@ -328,7 +328,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
     const uint32_t stream_bytes = kStaged ? ((uint32_t)kEntropyThreads * (uint32_t)subseq_bits / 8 + 63) / 16 * 16 + 16 : 0;
     const bool resident = kStaged && d.scan_len + 80 <= stream_bytes; // 64 zero bytes follow the stream
     uint8_t *cl = resident ? reinterpret_cast<uint8_t *>(s_stream) : clean + d.clean_off;
-    uint32_t clean_len = 0;
+    uint32_t clean_len = 0, flush_base = 0;
     // Every thread takes one aligned 16-byte word of the scan per pass (one load instead of sixteen);
     // the byte before it, which decides whether a leading 00 is stuffing, comes from the lane below.
     const uint32_t lead = (uint32_t)(reinterpret_cast<uintptr_t>(scan) & 15); // bytes of the first word before the scan
@@ -356,10 +356,37 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         int off = block_scan_exclusive(__popc(keep), s_warp, total);
         // byte k of the stream lives at address k ^ 3: every 32-bit word holds its bits MSB first
         uint32_t o = clean_len + off;
+        if (resident) {
 #pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (keep & (1u << i)) cl[(o++) ^ 3u] = b[i];
+            for (int i = 0; i < 16; i++)
+                if (keep & (1u << i)) cl[(o++) ^ 3u] = b[i];
+        } else {
+            // A stream that goes to global memory is collected in shared memory first (the stream
+            // buffer is free during this phase) and leaves as whole 16-byte vectors: one store per
+            // 16 bytes instead of one per byte.  flush_base (a multiple of 16) is the stream
+            // position of the buffer's first byte; fewer than 16 bytes stay behind per pass.
+            uint8_t *buf = reinterpret_cast<uint8_t *>(s_stream);
+#pragma unroll
+            for (int i = 0; i < 16; i++)
+                if (keep & (1u << i)) buf[((o++) - flush_base) ^ 3u] = b[i];
+            __syncthreads();
+            const uint32_t have = clean_len + (uint32_t)total - flush_base, nvec = have >> 4;
+            uint4 *dst16 = reinterpret_cast<uint4 *>(cl + flush_base);
+            const uint4 *src16 = reinterpret_cast<const uint4 *>(buf);
+            for (uint32_t k = tid; k < nvec; k += kEntropyThreads) dst16[k] = src16[k];
+            uint4 rest = make_uint4(0, 0, 0, 0);
+            if (tid == 0) rest = src16[nvec];
+            __syncthreads();
+            if (tid == 0) reinterpret_cast<uint4 *>(buf)[0] = rest; // the incomplete vector moves to the front
+            flush_base += nvec << 4;
+            // (the next pass's block scan has barriers between this store and the first byte written)
+        }
         clean_len += total;
+    }
+    if (!resident) { // what is left in the buffer: fewer than 16 bytes
+        __syncthreads();
+        if (tid < 16 && flush_base + tid < clean_len) cl[(flush_base + tid) ^ 3u] = reinterpret_cast<uint8_t *>(s_stream)[tid ^ 3u];
+        __syncthreads();
     }
     if (tid < 64) cl[(clean_len + tid) ^ 3u] = 0;
     __syncthreads();
@@ -775,7 +802,9 @@ void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_li
     if (n_list > 0) {
         const bool staged = subseq_bits <= kMaxStagedBits;
         auto launch = [&](auto kernel, int threads) {
-            const size_t smem = staged ? ((size_t)threads * subseq_bits / 8 + 63) / 16 * 16 + 16 : 16;
+            // (the non-staged variant uses the buffer only to collect the unstuffed stream: 16 bytes
+            // per thread and pass plus the incomplete vector carried over)
+            const size_t smem = staged ? ((size_t)threads * subseq_bits / 8 + 63) / 16 * 16 + 16 : (size_t)threads * 16 + 32;
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             kernel<<<n_list, threads, smem, stream>>>(descs, list, blob, huff, clean, coef, status, subseq_bits,
                                                       static_cast<CheckPoint *>(checkpoints), kCheckPointBits,
