@@ -11,11 +11,13 @@
 #include <string.h>
 #include <unistd.h>
 
+#include <array>
 #include <atomic>
 #include <condition_variable>
 #include <functional>
 #include <mutex>
 #include <string>
+#include <memory>
 #include <thread>
 #include <unordered_map>
 #include <chrono>
@@ -220,6 +222,8 @@ struct Slot {
     double stage_ms[4] = {0, 0, 0, 0}; // header parse, layout, payload copy, total
     std::vector<JpegHeader> headers;
     std::vector<uint64_t> table_hash; // per sample: hashes of its (DC, AC, quantisation) tables x 3 components
+    std::vector<uint16_t> table_id;   // per sample: the same nine tables as indices into the context's stores
+    std::vector<uint8_t> from_cache;  // per sample: its header came from the context's header cache
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     // payload gather runs on its own high-priority stream so that its few CTAs are placed ahead of
     // the large grids other slots have queued, and the PCIe transfer overlaps their compute
@@ -276,6 +280,22 @@ struct ffcvb_ctx {
         uint32_t subseq_bits;
         uint64_t created_seq;
     };
+    // Header cache: what the marker segments of a JPEG sample said, kept per sample (key: its
+    // offset in the file) so that from the second epoch on staging a sample is a table look-up
+    // instead of a parse; the few distinct Huffman and quantisation tables of a file live in a
+    // store of their own and the cache holds indices into it.
+    struct CachedHeader {
+        uint64_t size;
+        uint32_t scan_off, scan_len;
+        uint16_t restart_interval, width, height;
+        uint8_t ncomp, hs, vs;
+        uint16_t table[9]; // per component: DC, AC (huff_store), quantisation (quant_store)
+    };
+    bool cache_headers = false; // ffcvb_set_header_cache: sample offsets identify samples (one file per context)
+    std::unordered_map<uint64_t, CachedHeader> header_cache;
+    std::vector<std::unique_ptr<RawHuff>> huff_store;
+    std::vector<std::unique_ptr<std::array<uint16_t, 64>>> quant_store;
+    std::vector<uint64_t> huff_store_hash, quant_store_hash;
     DevBuf index_pool, index_stats;
     size_t index_used = 0;
     std::unordered_map<uint64_t, IndexEntry> index_map;
@@ -527,6 +547,8 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     s.src_ptrs.assign(ptrs, ptrs + n);
     s.headers.resize(n);
     s.table_hash.assign((size_t)n * 9, 0);
+    s.table_id.assign((size_t)n * 9, 0);
+    s.from_cache.assign((size_t)n, 0);
 
     // ---- reading from file descriptors: every sample's bytes get their place in the pinned buffer
     // before anything is parsed (a JPEG header can only be parsed once it has been read), so the
@@ -597,7 +619,25 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
         const uint8_t *src = from_fd ? s.host + spans[i].dst + spans[i].skip : file_base + ptrs[i];
         if (modes[i] == FFCVB_MODE_JPG) {
             JpegHeader &h = s.headers[i];
-            int rc = short_read ? kErrData : parse_jpeg_header(src, (size_t)sizes[i], &h);
+            int rc;
+            const auto hit = (short_read || !ctx->cache_headers) ? ctx->header_cache.end() : ctx->header_cache.find(ptrs[i]);
+            if (hit != ctx->header_cache.end() && hit->second.size == sizes[i]) {
+                // seen before: only the fields the layout needs are restored (the tables are in the store)
+                const ffcvb_ctx::CachedHeader &ch = hit->second;
+                h.width = ch.width;
+                h.height = ch.height;
+                h.ncomp = ch.ncomp;
+                h.hs[0] = ch.hs;
+                h.vs[0] = ch.vs;
+                h.scan_off = ch.scan_off;
+                h.scan_len = ch.scan_len;
+                h.restart_interval = ch.restart_interval;
+                for (int k = 0; k < 9; k++) s.table_id[(size_t)i * 9 + k] = ch.table[k];
+                s.from_cache[i] = 1;
+                rc = 0;
+            } else {
+                rc = short_read ? kErrData : parse_jpeg_header(src, (size_t)sizes[i], &h);
+            }
             if (rc == 0 && (h.width != d.width || h.height != d.height)) rc = kErrDims;
             d.host_status = (int16_t)rc;
             d.payload_size = (uint32_t)sizes[i];
@@ -634,7 +674,7 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
                     }
                 }
                 d.nblocks = (uint32_t)d.bpm * d.mcus_x * d.mcu_rows;
-                for (int c = 0; c < h.ncomp; c++) {
+                for (int c = 0; c < h.ncomp && !s.from_cache[i]; c++) {
                     uint64_t *th = &s.table_hash[(size_t)i * 9 + 3 * c];
                     // (bits[17] and vals[256] lie next to each other in RawHuff)
                     static_assert(offsetof(RawHuff, vals) == 17, "RawHuff: vals must follow bits");
@@ -725,10 +765,60 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
             }
         }
     }
-    // ---- serial: deduplicate tables, lay the blob out
+    // ---- serial: headers parsed just now enter the cache, their tables the store
+    for (int i = 0; i < n; i++) {
+        const ImageDesc &d = descs[i];
+        if (d.mode != FFCVB_MODE_JPG || d.host_status != 0 || s.from_cache[i]) continue;
+        const JpegHeader &h = s.headers[i];
+        uint16_t *ids = &s.table_id[(size_t)i * 9];
+        bool room = true;
+        for (int c = 0; c < h.ncomp; c++) {
+            const uint64_t *th = &s.table_hash[(size_t)i * 9 + 3 * c];
+            const RawHuff *tabs[2] = {&h.dc[h.td[c]], &h.ac[h.ta[c]]};
+            for (int k = 0; k < 2; k++) {
+                int found = -1;
+                for (int u = (int)ctx->huff_store.size() - 1; u >= 0 && found < 0; u--)
+                    if (ctx->huff_store_hash[u] == th[k] && memcmp(ctx->huff_store[u]->bits, tabs[k]->bits, 17) == 0) found = u;
+                if (found < 0 && ctx->huff_store.size() < 60000) {
+                    found = (int)ctx->huff_store.size();
+                    ctx->huff_store.emplace_back(new RawHuff(*tabs[k]));
+                    ctx->huff_store_hash.push_back(th[k]);
+                }
+                room = room && found >= 0;
+                ids[3 * c + k] = (uint16_t)(found < 0 ? 0 : found);
+            }
+            int qfound = -1;
+            for (int u = (int)ctx->quant_store.size() - 1; u >= 0 && qfound < 0; u--)
+                if (ctx->quant_store_hash[u] == th[2] && (*ctx->quant_store[u])[0] == h.quant[h.tq[c]][0]) qfound = u;
+            if (qfound < 0 && ctx->quant_store.size() < 60000) {
+                qfound = (int)ctx->quant_store.size();
+                ctx->quant_store.emplace_back(new std::array<uint16_t, 64>());
+                memcpy(ctx->quant_store.back()->data(), h.quant[h.tq[c]], 128);
+                ctx->quant_store_hash.push_back(th[2]);
+            }
+            room = room && qfound >= 0;
+            ids[3 * c + 2] = (uint16_t)(qfound < 0 ? 0 : qfound);
+        }
+        if (!room) return fail(ctx, FFCVB_E_LIMIT, "more than 60000 distinct Huffman or quantisation tables in a file");
+        if (ctx->cache_headers && ctx->header_cache.size() < (size_t)1 << 23) { // ~0.5 GB of host memory at most
+            ffcvb_ctx::CachedHeader ch{};
+            ch.size = sizes[i];
+            ch.scan_off = (uint32_t)h.scan_off;
+            ch.scan_len = (uint32_t)h.scan_len;
+            ch.restart_interval = (uint16_t)h.restart_interval;
+            ch.width = (uint16_t)h.width;
+            ch.height = (uint16_t)h.height;
+            ch.ncomp = (uint8_t)h.ncomp;
+            ch.hs = (uint8_t)h.hs[0];
+            ch.vs = (uint8_t)h.vs[0];
+            memcpy(ch.table, ids, sizeof(ch.table));
+            ctx->header_cache[ptrs[i]] = ch;
+        }
+    }
+    // ---- serial: the batch's own table lists (indices into the store -> indices into the blob)
     std::vector<const RawHuff *> huff_src;
     std::vector<const uint16_t *> mult_src;
-    std::vector<uint64_t> huff_hash, mult_hash;
+    std::vector<int> huff_of_store(ctx->huff_store.size(), -1), mult_of_store(ctx->quant_store.size(), -1);
     std::vector<int32_t> jpeg_list, par_list, seq_list;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes_par = 0;  // scan_bytes_par: largest scan
     uint32_t total_blocks = 0;
@@ -743,32 +833,23 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
             continue;
         }
         const JpegHeader &h = s.headers[i];
+        const uint16_t *ids = &s.table_id[(size_t)i * 9];
         for (int c = 0; c < h.ncomp; c++) {
-            const RawHuff *tabs[2] = {&h.dc[h.td[c]], &h.ac[h.ta[c]]};
             uint8_t *dst[2] = {&d.dc_tab[c], &d.ac_tab[c]};
-            const uint64_t *th = &s.table_hash[(size_t)i * 9 + 3 * c];
             for (int k = 0; k < 2; k++) {
-                // same 64-bit hash and same code-length counts: taken to be the same table
-                int found = -1;
-                for (int u = (int)huff_src.size() - 1; u >= 0 && found < 0; u--)
-                    if (huff_hash[u] == th[k] && (huff_src[u] == tabs[k] || memcmp(huff_src[u]->bits, tabs[k]->bits, 17) == 0))
-                        found = u;
-                if (found < 0) {
-                    found = (int)huff_src.size();
-                    huff_src.push_back(tabs[k]);
-                    huff_hash.push_back(th[k]);
+                int &slot_of = huff_of_store[ids[3 * c + k]];
+                if (slot_of < 0) {
+                    slot_of = (int)huff_src.size();
+                    huff_src.push_back(ctx->huff_store[ids[3 * c + k]].get());
                 }
-                *dst[k] = (uint8_t)found;
+                *dst[k] = (uint8_t)slot_of;
             }
-            int qfound = -1;
-            for (int u = (int)mult_src.size() - 1; u >= 0 && qfound < 0; u--)
-                if (mult_hash[u] == th[2] && mult_src[u][0] == h.quant[h.tq[c]][0]) qfound = u;
-            if (qfound < 0) {
-                qfound = (int)mult_src.size();
-                mult_src.push_back(h.quant[h.tq[c]]);
-                mult_hash.push_back(th[2]);
+            int &qslot = mult_of_store[ids[3 * c + 2]];
+            if (qslot < 0) {
+                qslot = (int)mult_src.size();
+                mult_src.push_back(ctx->quant_store[ids[3 * c + 2]]->data());
             }
-            d.q_tab[c] = (uint8_t)qfound;
+            d.q_tab[c] = (uint8_t)qslot;
         }
         if (huff_src.size() > 255 || mult_src.size() > 255)
             return fail(ctx, FFCVB_E_LIMIT, "more than 255 distinct Huffman or quantisation tables in a batch");
@@ -1229,6 +1310,14 @@ int ffcvb_set_batch_riders(ffcvb_ctx *ctx, int slot, const ffcvb_rider *riders, 
         }
         s.pending_riders.push_back(std::move(r));
     }
+    return FFCVB_OK;
+}
+
+int ffcvb_set_header_cache(ffcvb_ctx *ctx, int enabled) {
+    if (!ctx) return FFCVB_E_ARG;
+    ctx->pool->wait_all();
+    ctx->cache_headers = enabled != 0;
+    ctx->header_cache.clear();
     return FFCVB_OK;
 }
 

@@ -61,6 +61,8 @@ lib.ffcvb_submit_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_submit_batch.restype = c_int
 lib.ffcvb_rerun_batch.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
 lib.ffcvb_rerun_batch.restype = c_int
+lib.ffcvb_set_header_cache.argtypes = [c_void_p, c_int]
+lib.ffcvb_set_header_cache.restype = c_int
 lib.ffcvb_set_decode_index.argtypes = [c_void_p, c_uint64]
 lib.ffcvb_set_decode_index.restype = c_int
 lib.ffcvb_decode_index_stats.argtypes = [c_void_p, c_void_p]
@@ -247,6 +249,10 @@ class Context:
 
     def staging_split(self):
         return int(lib.ffcvb_staging_split(self._h))
+
+    def set_header_cache(self, enabled):
+        """Remember parsed JPEG headers per sample offset (the context then serves one file)."""
+        self._check(lib.ffcvb_set_header_cache(self._h, int(bool(enabled))), 'ffcvb_set_header_cache')
 
     def set_decode_index(self, nbytes):
         """Device memory for the decode index (0: off); see ffcvb_set_decode_index."""

@@ -237,6 +237,8 @@ class Loader:
             self._contexts[index] = L.Context(index[0], n_slots=self.batches_ahead + 2, n_threads=threads)
             # the payload copy of a batch overlaps the drawing of the next batch's parameters
             self._contexts[index].set_async_staging(True)
+            # this context only ever sees this loader's file: parsed headers are kept per sample
+            self._contexts[index].set_header_cache(True)
             if self.pin_file:
                 self._contexts[index].set_staging_split(self.stage_split)
             if self.decode_index_gb > 0:

@@ -150,6 +150,13 @@ typedef struct {
 } ffcvb_rider;
 int ffcvb_set_batch_riders(ffcvb_ctx *ctx, int slot, const ffcvb_rider *riders, int n_riders, int n);
 
+/* Header cache (no counterpart in the reference).  When enabled the context remembers, per sample
+ * (told apart by its offset in the file, so the context must then serve ONE file whose bytes do not
+ * change), what the marker segments of its JPEG stream said; staging the sample again is then a
+ * table look-up instead of a parse.  About 50 bytes of host memory per JPEG sample seen, at most
+ * 8 M samples.  Off by default (the single-image entry points pass every stream at offset 0). */
+int ffcvb_set_header_cache(ffcvb_ctx *ctx, int enabled);
+
 /* Decode index (no counterpart in the reference).  A loader decodes the same JPEG streams epoch
  * after epoch, and what makes the decode of a stream without restart markers expensive on a GPU
  * -- finding the decoder's state at the start of every subsequence -- is the same every time.
