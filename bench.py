@@ -18,7 +18,8 @@ One JSON line on stdout (rank 0):
   e2e        images/s through `for batch in Loader(...)`: host staging from the file, host->device
              copy, kernels, and an 8-byte device->host read per step.  Timed in the steady state:
              the batches the loader had prepared ahead while this process waited are consumed
-             before the clock starts, and at least `e2e.steps_timed` >= K steps are timed
+             before the clock starts, and at least `e2e.steps_timed` >= K steps are timed, as three
+             segments of which the median counts (the host's memory and PCIe are shared)
   roofline   the dominant kernel against the bound that binds it (instruction issue), with the
              HBM figure beside it; per-kernel instruction and DRAM-traffic figures come from the
              ncu captures summarised in profiles/ncu_constants.json (`profile_stale` tells whether
@@ -449,31 +450,39 @@ class Bench:
             timed = int(self.max_over_ranks([timed])[0])
         if sampler is not None:
             sampler.start()
-        e0, e1 = ch.cuda.Event(enable_timing=True), ch.cuda.Event(enable_timing=True)
+        # The timed steps are taken as three consecutive segments and the median segment is the
+        # result: the host side of this path (DRAM and PCIe) is shared with whatever else runs on
+        # the machine, and a neighbour's burst would otherwise decide the figure.
+        timed = (timed + 2) // 3 * 3
+        marks = [ch.cuda.Event(enable_timing=True) for _ in range(4)]
         h2d, stage, gather = [], [], []
-        e0.record()
+        marks[0].record()
         for k in range(timed):
             digest += consume()
             h2d.append(exe.h2d_bytes)
             if k % 8 == 0:
                 stage.append(exe.ctx.stage_times(k % (loader.batches_ahead + 2)))
-        e1.record()
+            if (k + 1) % (timed // 3) == 0:
+                marks[(k + 1) // (timed // 3)].record()
         ch.cuda.synchronize()
         self.barrier()
+        segments = [marks[i].elapsed_time(marks[i + 1]) for i in range(3)]
         for s in range(loader.batches_ahead + 2):
             g = exe.ctx.gather_time(s)
             if g is not None:
                 gather.append(g)
         loader._live_iterator.retire()
-        return dict(ms=e0.elapsed_time(e1), steps=timed, h2d=int(np.mean(h2d)), launches=exe.launches, digest=digest,
+        return dict(ms=float(np.median(segments)) * 3, segments=[v / (timed // 3) for v in segments], steps=timed,
+                    h2d=int(np.mean(h2d)), launches=exe.launches, digest=digest,
                     stage_ms=np.mean(np.array(stage), axis=0) if stage else np.zeros(4),
                     gather_ms=float(np.mean(gather)) if gather else None, batch=batch)
 
     def e2e_entry(self, res, loader=None, source=None):
         ms = self.max_over_ranks([res['ms']])[0]
         entry = {'value': res['batch'] * self.world * res['steps'] / (ms * 1e-3), 'unit': 'images/s',
-                 'ms_per_step': ms / res['steps'], 'steps_timed': res['steps'], 'h2d_bytes_per_step': res['h2d'],
-                 'd2h_bytes_per_step': 8}
+                 'ms_per_step': ms / res['steps'], 'steps_timed': res['steps'],
+                 'segments_ms_per_step': res['segments'],  # rank 0's three segments; the median one counts
+                 'h2d_bytes_per_step': res['h2d'], 'd2h_bytes_per_step': 8}
         if source is not None:
             entry['source'] = source
         return entry
