@@ -356,14 +356,16 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         int off = block_scan_exclusive(__popc(keep), s_warp, total);
         // byte k of the stream lives at address k ^ 3: every 32-bit word holds its bits MSB first
         uint32_t o = clean_len + off;
-        if (resident) {
+        if (kStaged) {
+            // into the stream buffer in shared memory (or, for the rare scan that does not fit it,
+            // byte by byte into the scratch buffer)
 #pragma unroll
             for (int i = 0; i < 16; i++)
                 if (keep & (1u << i)) cl[(o++) ^ 3u] = b[i];
         } else {
-            // A stream that goes to global memory is collected in shared memory first (the stream
-            // buffer is free during this phase) and leaves as whole 16-byte vectors: one store per
-            // 16 bytes instead of one per byte.  flush_base (a multiple of 16) is the stream
+            // The variant for multi-megabit scans keeps the stream in global memory: it is collected
+            // in shared memory first and leaves as whole 16-byte vectors, one store per 16 bytes
+            // instead of one per byte.  flush_base (a multiple of 16) is the stream
             // position of the buffer's first byte; fewer than 16 bytes stay behind per pass.
             uint8_t *buf = reinterpret_cast<uint8_t *>(s_stream);
 #pragma unroll
@@ -383,7 +385,7 @@ entropy_parallel_kernel(const ImageDesc *__restrict__ descs, const int32_t *__re
         }
         clean_len += total;
     }
-    if (!resident) { // what is left in the buffer: fewer than 16 bytes
+    if (!kStaged) { // what is left in the buffer: fewer than 16 bytes
         __syncthreads();
         if (tid < 16 && flush_base + tid < clean_len) cl[(flush_base + tid) ^ 3u] = reinterpret_cast<uint8_t *>(s_stream)[tid ^ 3u];
         __syncthreads();
