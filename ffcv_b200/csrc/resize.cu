@@ -71,8 +71,9 @@ __device__ __forceinline__ void linear_taps(int d, int ssize, double inv, double
 
 __device__ __forceinline__ int sat_round(float v) { return min(255, max(0, __float2int_rn(v))); }
 
-// Exact uint8 -> float without the conversion pipe: 2^23 + v is representable, subtract 2^23.
-__device__ __forceinline__ float u8f(uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.0f; }
+// uint8 -> float without the conversion pipe: 2^23 + v is representable; the 2^23 is taken off again
+// inside the multiplication, fma(2^23 + v, w, -2^23 * w)
+__device__ __forceinline__ float u8biased(uint32_t v) { return __uint_as_float(0x4B000000u | v); }
 
 // Per-axis tap tables in shared memory, computed once per CTA (double-precision position
 // arithmetic as OpenCV does it, then only fp32 / integer work per pixel).
@@ -152,7 +153,7 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
 
     const int i = blockIdx.y;
     if (!kU8)
-        for (int k = threadIdx.x; k < 768; k += blockDim.x) s_lut[k] = lut[k];
+        for (int k = threadIdx.x; k < 768; k += blockDim.x) s_lut[(k % 3) * 256 + k / 3] = lut[k]; // per channel
 
     // ---- where the sample's pixels are
     const uint8_t *base;
@@ -246,17 +247,26 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
         }
         return filled;
     };
-    auto emit = [&](int pix, const int *val) { // normalise (table gather) into the shared tile, in final memory order
+    // normalise (table gather, one 256-entry table per channel) into the shared tile, in final
+    // memory order: element = pix * pix_step + c * chan_step
+    int pix_step = 3, chan_step = 1;
+    auto emit = [&](int pix, const int *val) {
+        OutT *o = s_out + pix * pix_step;
 #pragma unroll
         for (int c = 0; c < 3; c++) {
-            OutT v;
             if constexpr (kU8)
-                v = (OutT)val[c];
+                o[c * chan_step] = (OutT)val[c];
             else
-                v = s_lut[val[c] * 3 + c];
-            s_out[planar ? c * npix + pix : pix * 3 + c] = v;
+                o[c * chan_step] = s_lut[c * 256 + val[c]];
         }
     };
+    // With flips only (or no augmentation) nothing is ever filled and the column an output column
+    // comes from does not depend on the row: the trace is done once per column.
+    bool flips_only = true;
+    for (int k = 0; k < ops.n_ops; k++) flips_only = flips_only && ops.type[k] == kOpFlip;
+    bool mirrored = false;
+    if (flips_only)
+        for (int k = 0; k < ops.n_ops; k++) mirrored ^= prm[4 + 2 * k] != 0;
     // A CTA produces every gridDim.x-th band of its image: what was set up above (descriptor, tap
     // tables, lookup table) serves all of them.
     const int nbands = (out_h + band_rows - 1) / band_rows;
@@ -264,6 +274,8 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     band0 = band * band_rows;
     rows = min(band_rows, out_h - band0);
     npix = rows * out_w;
+    pix_step = planar ? 1 : 3;
+    chan_step = planar ? npix : 1;
     if (regime == kArea && ok) {
         // Shrinking by fractional factors is separable: OpenCV first sums every source row
         // horizontally with the x weights, then combines those row sums with the y weights.  A
@@ -275,58 +287,127 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
         for (int t = threadIdx.x; t < groups * out_w; t += blockDim.x) {
             const int g = (int)__umulhi((uint32_t)t, inv_w), ox = t - g * out_w;
             const int r_end = min(rows, (g + 1) * run);
-            int cx = -1, xf = 0, xn = 0;     // column whose taps are loaded
-            float w_first = 0.f, w_mid = 0.f, w_last = 0.f;
+            int cx = -1, xoff = 0, xmid = 0, xlast = 0; // column whose taps are loaded
+            bool two = false;
+            float w_first = 0.f, w_mid = 0.f, w_last = 0.f, c_first = 0.f, c_mid = 0.f, c_last = 0.f;
             int pj = -1;                       // source row whose horizontal sums are held
             float p0 = 0.f, p1 = 0.f, p2 = 0.f;
+            const int x_plain = mirrored ? out_w - 1 - ox : ox;
+            // horizontal sums of one source row: first tap, the whole cells between, last tap.
+            // fma(2^23 + v, w, -2^23 * w) is the correctly rounded v * w, exactly what the
+            // multiplication of the converted value gives (2^23 * w is exact).
+            auto across = [&](int row) {
+                const uint8_t *p = row_ptr(row) + xoff;
+                p0 = __fmaf_rn(u8biased(p[0]), w_first, c_first);
+                p1 = __fmaf_rn(u8biased(p[1]), w_first, c_first);
+                p2 = __fmaf_rn(u8biased(p[2]), w_first, c_first);
+                const uint8_t *q = p + 3;
+                for (int k = 0; k < xmid; k++, q += 3) {
+                    p0 = __fadd_rn(p0, __fmaf_rn(u8biased(q[0]), w_mid, c_mid));
+                    p1 = __fadd_rn(p1, __fmaf_rn(u8biased(q[1]), w_mid, c_mid));
+                    p2 = __fadd_rn(p2, __fmaf_rn(u8biased(q[2]), w_mid, c_mid));
+                }
+                if (two) {
+                    p0 = __fadd_rn(p0, __fmaf_rn(u8biased(p[xlast]), w_last, c_last));
+                    p1 = __fadd_rn(p1, __fmaf_rn(u8biased(p[xlast + 1]), w_last, c_last));
+                    p2 = __fadd_rn(p2, __fmaf_rn(u8biased(p[xlast + 2]), w_last, c_last));
+                }
+            };
             for (int r = g * run; r < r_end; r++) {
-                int y, x, val[3] = {0, 0, 0};
-                if (!trace(band0 + r, ox, y, x, val)) {
+                int y = band0 + r, x = x_plain, val[3] = {0, 0, 0};
+                if (flips_only || !trace(band0 + r, ox, y, x, val)) {
                     if (x != cx) {
                         cx = x;
                         pj = -1;
-                        xf = tx.first[x];
-                        const int xc = tx.count[x];
-                        xn = xc & 0xffff;
+                        const int xc = tx.count[x], xn = xc & 0xffff;
                         const bool xl = xc & (1 << 16), xr = xc & (1 << 17);
+                        xoff = tx.first[x] * 3;
                         w_mid = tx.wm[x];
                         w_last = xr ? tx.wr[x] : w_mid;
                         w_first = xl ? tx.wl[x] : (xn == 1 ? w_last : w_mid);
+                        two = xn >= 2;
+                        xmid = max(xn - 2, 0);
+                        xlast = (xn - 1) * 3;
+                        c_first = -8388608.0f * w_first;
+                        c_mid = -8388608.0f * w_mid;
+                        c_last = -8388608.0f * w_last;
                     }
                     const int yf = ty.first[y], yc = ty.count[y], yn = yc & 0xffff;
                     const float ywm = ty.wm[y];
                     const float y_last = (yc & (1 << 17)) ? ty.wr[y] : ywm;
                     const float y_first = (yc & (1 << 16)) ? ty.wl[y] : (yn == 1 ? y_last : ywm);
-                    float a0 = 0.f, a1 = 0.f, a2 = 0.f;
-                    for (int j = 0; j < yn; j++) {
-                        if (yf + j != pj) {
-                            pj = yf + j;
-                            const uint8_t *p = row_ptr(pj) + xf * 3;
-                            p0 = __fmul_rn(u8f(p[0]), w_first);
-                            p1 = __fmul_rn(u8f(p[1]), w_first);
-                            p2 = __fmul_rn(u8f(p[2]), w_first);
-                            p += 3;
-                            for (int k = 1; k < xn; k++, p += 3) {
-                                const float w = k == xn - 1 ? w_last : w_mid;
-                                p0 = __fadd_rn(p0, __fmul_rn(u8f(p[0]), w));
-                                p1 = __fadd_rn(p1, __fmul_rn(u8f(p[1]), w));
-                                p2 = __fadd_rn(p2, __fmul_rn(u8f(p[2]), w));
-                            }
-                        }
-                        const float beta = j == 0 ? y_first : (j == yn - 1 ? y_last : ywm);
-                        if (j == 0) {
-                            a0 = __fmul_rn(beta, p0);
-                            a1 = __fmul_rn(beta, p1);
-                            a2 = __fmul_rn(beta, p2);
-                        } else {
-                            a0 = __fadd_rn(a0, __fmul_rn(beta, p0));
-                            a1 = __fadd_rn(a1, __fmul_rn(beta, p1));
-                            a2 = __fadd_rn(a2, __fmul_rn(beta, p2));
-                        }
+                    // only the first source row can be the one the previous output row ended with
+                    if (yf != pj) across(yf);
+                    float a0 = __fmul_rn(y_first, p0), a1 = __fmul_rn(y_first, p1), a2 = __fmul_rn(y_first, p2);
+                    for (int j = 1; j < yn; j++) {
+                        across(yf + j);
+                        const float beta = j == yn - 1 ? y_last : ywm;
+                        a0 = __fadd_rn(a0, __fmul_rn(beta, p0));
+                        a1 = __fadd_rn(a1, __fmul_rn(beta, p1));
+                        a2 = __fadd_rn(a2, __fmul_rn(beta, p2));
                     }
+                    pj = yf + yn - 1;
                     val[0] = sat_round(a0);
                     val[1] = sat_round(a1);
                     val[2] = sat_round(a2);
+                }
+                emit(r * out_w + ox, val);
+            }
+        }
+    } else if (regime == kLinear && ok) {
+        // Enlarging (OpenCV's fixed-point bilinear) with the same ownership: the two taps of the
+        // column stay in registers, and of the two source rows an output row blends, the next
+        // output row nearly always shares one or both, whose horizontally interpolated values
+        // are kept instead of being fetched and interpolated again.
+        const int run = (rows + groups - 1) / groups;
+        for (int t = threadIdx.x; t < groups * out_w; t += blockDim.x) {
+            const int g = (int)__umulhi((uint32_t)t, inv_w), ox = t - g * out_w;
+            const int r_end = min(rows, (g + 1) * run);
+            int cx = -1, o0 = 0, o1 = 0, xa0 = 0, xa1 = 0;
+            int ra = -1, rb = -1; // source rows whose interpolated values ha / hb hold
+            int ha[3] = {0, 0, 0}, hb[3] = {0, 0, 0};
+            const int x_plain = mirrored ? out_w - 1 - ox : ox;
+            for (int r = g * run; r < r_end; r++) {
+                int y = band0 + r, x = x_plain, val[3] = {0, 0, 0};
+                if (flips_only || !trace(band0 + r, ox, y, x, val)) {
+                    if (x != cx) {
+                        cx = x;
+                        ra = rb = -1;
+                        const int sx = tx.first[x], xw = tx.count[x];
+                        xa0 = xw >> 16;
+                        xa1 = xw & 0xffff;
+                        o0 = 3 * sx;
+                        o1 = 3 * min(sx + 1, cw - 1);
+                    }
+                    const int sy = ty.first[y], yw = ty.count[y], b0 = yw >> 16, b1 = yw & 0xffff;
+                    const int ry0 = min(sy, ch - 1), ry1 = min(sy + 1, ch - 1);
+                    auto across = [&](int row, int *h) {
+                        const uint8_t *S = row_ptr(row);
+#pragma unroll
+                        for (int c = 0; c < 3; c++) h[c] = (S[o0 + c] * xa0 + S[o1 + c] * xa1) >> 4;
+                    };
+                    // rows only move forward: the upper row is the former upper or lower one
+                    // (selects, no branch), or both rows are new
+                    if (ry0 == rb) {
+#pragma unroll
+                        for (int c = 0; c < 3; c++) ha[c] = hb[c];
+                    } else if (ry0 != ra) {
+                        across(ry0, ha);
+                    }
+                    if (ry1 == ry0) {
+#pragma unroll
+                        for (int c = 0; c < 3; c++) hb[c] = ha[c];
+                    } else if (ry1 != rb) {
+                        across(ry1, hb);
+                    }
+                    ra = ry0;
+                    rb = ry1;
+#pragma unroll
+                    for (int c = 0; c < 3; c++) {
+                        // non-negative terms: only the upper bound can be exceeded (by rounding of the weights)
+                        const int v = (((b0 * ha[c]) >> 16) + ((b1 * hb[c]) >> 16) + 2) >> 2;
+                        val[c] = min(255, v);
+                    }
                 }
                 emit(r * out_w + ox, val);
             }
@@ -360,19 +441,6 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
                         val[0] = sat_round(__fmul_rn((float)s0, inv));
                         val[1] = sat_round(__fmul_rn((float)s1, inv));
                         val[2] = sat_round(__fmul_rn((float)s2, inv));
-                    }
-                } else if (regime == kLinear) {
-                    const int sx = tx.first[x], xw = tx.count[x], xa0 = xw >> 16, xa1 = xw & 0xffff;
-                    const int sy = ty.first[y], yw = ty.count[y], b0 = yw >> 16, b1 = yw & 0xffff;
-                    const int sx1 = min(sx + 1, cw - 1);
-                    const int ry0 = min(sy, ch - 1), ry1 = min(sy + 1, ch - 1);
-                    const uint8_t *S0 = row_ptr(ry0), *S1 = row_ptr(ry1);
-#pragma unroll
-                    for (int c = 0; c < 3; c++) {
-                        const int h0 = S0[3 * sx + c] * xa0 + S0[3 * sx1 + c] * xa1;
-                        const int h1 = S1[3 * sx + c] * xa0 + S1[3 * sx1 + c] * xa1;
-                        const int v = (((b0 * (h0 >> 4)) >> 16) + ((b1 * (h1 >> 4)) >> 16) + 2) >> 2;
-                        val[c] = min(255, max(0, v));
                     }
                 }
             }
