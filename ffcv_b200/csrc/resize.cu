@@ -20,6 +20,8 @@
 // output rows that touch it.
 #include <float.h>
 
+#include <type_traits>
+
 #include "kernels.h"
 
 namespace ffcvb {
@@ -27,6 +29,7 @@ namespace ffcvb {
 enum { kOpFlip = 1, kOpTranslate = 2, kOpCutout = 3 };
 enum { kOutU8 = 0, kOutF16Nhwc = 1, kOutF16Nchw = 2, kOutF32Nhwc = 3, kOutF32Nchw = 4 };
 enum { kCopy = 0, kInteger = 1, kArea = 2, kLinear = 3 };
+constexpr int kMaxWindowRows = 96; // source rows of a band that can be staged in shared memory
 
 struct AreaTaps {
     int first, n;
@@ -131,12 +134,13 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
 resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *__restrict__ params, int n_params,
                       const __grid_constant__ OpList ops,
-                      int resize, int out_h, int out_w, int band_rows, int groups, int planar,
+                      int resize, int out_h, int out_w, int band_rows, int groups, int planar, int win_bytes,
                       const OutT *__restrict__ lut, OutT *__restrict__ out,
                       const int32_t *__restrict__ status) {
     extern __shared__ __align__(16) unsigned char s_raw[];
     constexpr bool kU8 = sizeof(OutT) == 1;
-    // shared layout: [out tile][lut][x taps (5 arrays of out_w)][y taps (5 arrays of ny)]
+    // shared layout: [out tile][lut][x taps (5 arrays of out_w)][y taps (5 arrays of out_h)]
+    //                [start of each window row][window of source rows (win_bytes)]
     int band0 = 0, rows = 0; // the band of output rows being produced (see the loop below)
     const int tile_elems = band_rows * out_w * 3;
     OutT *s_out = reinterpret_cast<OutT *>(s_raw);
@@ -150,6 +154,9 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     int *jbase = ibase + 5 * out_w;
     TapTables ty{jbase, jbase + out_h, reinterpret_cast<float *>(jbase + 2 * out_h),
                  reinterpret_cast<float *>(jbase + 3 * out_h), reinterpret_cast<float *>(jbase + 4 * out_h)};
+    int *s_rowoff = jbase + 5 * out_h;
+    unsigned char *s_win =
+        s_raw + ((off + sizeof(int) * (5 * ((size_t)out_w + out_h) + kMaxWindowRows) + 15) & ~(size_t)15);
 
     const int i = blockIdx.y;
     if (!kU8)
@@ -267,6 +274,8 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     bool mirrored = false;
     if (flips_only)
         for (int k = 0; k < ops.n_ops; k++) mirrored ^= prm[4 + 2 * k] != 0;
+    bool rows_in_place = true; // no translation: output row y comes from row y of the resized crop
+    for (int k = 0; k < ops.n_ops; k++) rows_in_place = rows_in_place && ops.type[k] != kOpTranslate;
     // A CTA produces every gridDim.x-th band of its image: what was set up above (descriptor, tap
     // tables, lookup table) serves all of them.
     const int nbands = (out_h + band_rows - 1) / band_rows;
@@ -276,6 +285,37 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     npix = rows * out_w;
     pix_step = planar ? 1 : 3;
     chan_step = planar ? npix : 1;
+    // The source rows this band reads are staged in shared memory first, when they fit: whole
+    // 16-byte words, many in flight per thread, instead of byte loads that each wait for a first
+    // touch of their sector in L2 or HBM.  The window keeps every row at its 16-byte phase.
+    bool staged = false;
+    int win_lo = 0;
+    if (win_bytes > 0 && rows_in_place && ok && (regime == kArea || regime == kLinear)) {
+        const int yb = band0 + rows - 1;
+        int hi;
+        if (regime == kArea) {
+            win_lo = ty.first[band0];
+            hi = ty.first[yb] + (ty.count[yb] & 0xffff) - 1;
+        } else {
+            win_lo = min(ty.first[band0], ch - 1);
+            hi = min(ty.first[yb] + 1, ch - 1);
+        }
+        const int nrows = hi - win_lo + 1, pitch = ((cw * 3 + 15) & ~15) + 16;
+        if (nrows <= kMaxWindowRows && nrows * pitch <= win_bytes) {
+            staged = true;
+            const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            for (int row = warp; row < nrows; row += blockDim.x >> 5) {
+                const uint8_t *p = row_ptr(win_lo + row);
+                const uint32_t phase = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 15);
+                const uint4 *g = reinterpret_cast<const uint4 *>(p - phase);
+                uint4 *d = reinterpret_cast<uint4 *>(s_win + row * pitch);
+                const int chunks = (int)(phase + cw * 3 + 15) >> 4;
+                for (int k = lane; k < chunks; k += 32) d[k] = __ldg(g + k);
+                if (lane == 0) s_rowoff[row] = row * pitch + (int)phase;
+            }
+            __syncthreads();
+        }
+    }
     if (regime == kArea && ok) {
         // Shrinking by fractional factors is separable: OpenCV first sums every source row
         // horizontally with the x weights, then combines those row sums with the y weights.  A
@@ -284,6 +324,7 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
         // a source row that two neighbouring output rows share (the row their boundary cuts) is
         // computed once.  Same operations in the same order as the per-pixel form, so the same bits.
         const int run = (rows + groups - 1) / groups;
+        auto area_columns = [&](auto from_window) {
         for (int t = threadIdx.x; t < groups * out_w; t += blockDim.x) {
             const int g = (int)__umulhi((uint32_t)t, inv_w), ox = t - g * out_w;
             const int r_end = min(rows, (g + 1) * run);
@@ -297,7 +338,11 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
             // fma(2^23 + v, w, -2^23 * w) is the correctly rounded v * w, exactly what the
             // multiplication of the converted value gives (2^23 * w is exact).
             auto across = [&](int row) {
-                const uint8_t *p = row_ptr(row) + xoff;
+                const uint8_t *p;
+                if constexpr (decltype(from_window)::value)
+                    p = s_win + s_rowoff[row - win_lo] + xoff;
+                else
+                    p = row_ptr(row) + xoff;
                 p0 = __fmaf_rn(u8biased(p[0]), w_first, c_first);
                 p1 = __fmaf_rn(u8biased(p[1]), w_first, c_first);
                 p2 = __fmaf_rn(u8biased(p[2]), w_first, c_first);
@@ -354,12 +399,18 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
                 emit(r * out_w + ox, val);
             }
         }
+        };
+        if (staged)
+            area_columns(std::true_type{});
+        else
+            area_columns(std::false_type{});
     } else if (regime == kLinear && ok) {
         // Enlarging (OpenCV's fixed-point bilinear) with the same ownership: the two taps of the
         // column stay in registers, and of the two source rows an output row blends, the next
         // output row nearly always shares one or both, whose horizontally interpolated values
         // are kept instead of being fetched and interpolated again.
         const int run = (rows + groups - 1) / groups;
+        auto linear_columns = [&](auto from_window) {
         for (int t = threadIdx.x; t < groups * out_w; t += blockDim.x) {
             const int g = (int)__umulhi((uint32_t)t, inv_w), ox = t - g * out_w;
             const int r_end = min(rows, (g + 1) * run);
@@ -382,7 +433,11 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
                     const int sy = ty.first[y], yw = ty.count[y], b0 = yw >> 16, b1 = yw & 0xffff;
                     const int ry0 = min(sy, ch - 1), ry1 = min(sy + 1, ch - 1);
                     auto across = [&](int row, int *h) {
-                        const uint8_t *S = row_ptr(row);
+                        const uint8_t *S;
+                        if constexpr (decltype(from_window)::value)
+                            S = s_win + s_rowoff[row - win_lo];
+                        else
+                            S = row_ptr(row);
 #pragma unroll
                         for (int c = 0; c < 3; c++) h[c] = (S[o0 + c] * xa0 + S[o1 + c] * xa1) >> 4;
                     };
@@ -412,6 +467,11 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
                 emit(r * out_w + ox, val);
             }
         }
+        };
+        if (staged)
+            linear_columns(std::true_type{});
+        else
+            linear_columns(std::false_type{});
     } else {
         for (int pix = threadIdx.x; pix < npix; pix += blockDim.x) {
             const int r = (int)__umulhi((uint32_t)pix, inv_w), ox = pix - r * out_w;
@@ -478,10 +538,16 @@ static void launch_typed(const ResizeSource &src, int n, const int32_t *params, 
     auto smem_for = [&](int b) {
         size_t tile = (((size_t)b * out_w * 3 * sizeof(OutT)) + 15) & ~(size_t)15;
         size_t lutb = (768 * sizeof(OutT) + 15) & ~(size_t)15;
-        return tile + lutb + sizeof(int) * 5 * ((size_t)out_w + out_h);
+        return ((tile + lutb + sizeof(int) * (5 * ((size_t)out_w + out_h) + kMaxWindowRows)) + 15) & ~(size_t)15;
     };
     while (band > 1 && smem_for(band) > 200 * 1024) band /= 2;
-    const size_t smem = smem_for(band);
+    // window of source rows: what is left of a quarter of the SM's shared memory (four resident
+    // CTAs of 256 threads is what the registers allow), at most 32 KiB
+    const size_t quarter = (227 * 1024) / 4 - 1024;
+    size_t win = smem_for(band) + 4096 <= quarter ? quarter - smem_for(band) : 0;
+    if (win > 32 * 1024) win = 32 * 1024;
+    win &= ~(size_t)15;
+    const size_t smem = smem_for(band) + win;
     auto kern = resize_augment_kernel<OutT>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     // CTAs per image: enough of them for about eight waves of the GPU (148 SMs x 4 resident CTAs;
@@ -504,7 +570,7 @@ static void launch_typed(const ResizeSource &src, int n, const int32_t *params, 
         }
     }
     kern<<<grid, 256, smem, stream>>>(src, params, n_params, ops, resize, out_h, out_w, band, groups, planar,
-                                      (const OutT *)lut, (OutT *)out, status);
+                                      (int)win, (const OutT *)lut, (OutT *)out, status);
 }
 
 void launch_resize_augment(const ResizeSource &src, int n, const int32_t *params, int n_params,
