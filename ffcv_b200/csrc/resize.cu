@@ -40,6 +40,15 @@ struct AreaTaps {
     }
 };
 
+// a / b correctly rounded, given the correctly rounded 1 / b: the product with the reciprocal is
+// within 1.5 ulp, a first remainder step makes it faithful, a second one correctly rounded
+// (Markstein); three double-precision divisions per tap would otherwise dominate the CTA's set-up.
+__device__ __forceinline__ double quotient(double a, double b, double inv_b) {
+    double q = a * inv_b;
+    q = fma(fma(-b, q, a), inv_b, q);
+    return fma(fma(-b, q, a), inv_b, q);
+}
+
 // Source cells covering destination cell d of an axis shrunk by `scale` (>= 1).
 __device__ __forceinline__ AreaTaps area_taps(int d, int ssize, double scale) {
     AreaTaps t;
@@ -50,9 +59,10 @@ __device__ __forceinline__ AreaTaps area_taps(int d, int ssize, double scale) {
     s1 = min(s1, s2);
     t.has_l = (s1 - f1) > 1e-3;
     t.has_r = (f2 - s2) > 1e-3;
-    t.wl = (float)((s1 - f1) / cell);
-    t.wm = (float)(1.0 / cell);
-    t.wr = (float)(fmin(fmin(f2 - s2, 1.0), cell) / cell);
+    const double inv_cell = 1.0 / cell;
+    t.wl = (float)quotient(s1 - f1, cell, inv_cell);
+    t.wm = (float)inv_cell;
+    t.wr = (float)quotient(fmin(fmin(f2 - s2, 1.0), cell), cell, inv_cell);
     t.first = t.has_l ? s1 - 1 : s1;
     t.n = (t.has_l ? 1 : 0) + (s2 - s1) + (t.has_r ? 1 : 0);
     return t;
@@ -206,15 +216,38 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     } else {
         ok = ok && img_h == out_h && img_w == out_w;
     }
+    // With flips only (or no augmentation) nothing is ever filled and the column an output column
+    // comes from does not depend on the row: the trace is done once per column.
+    bool flips_only = true;
+    for (int k = 0; k < ops.n_ops; k++) flips_only = flips_only && ops.type[k] == kOpFlip;
+    bool rows_in_place = true; // no translation: output row y comes from row y of the resized crop
+    for (int k = 0; k < ops.n_ops; k++) rows_in_place = rows_in_place && ops.type[k] != kOpTranslate;
+
+    // The scale factors (four double-precision divisions) are worked out by one thread.
+    __shared__ Scaling s_scaling;
+    if (threadIdx.x == 0 && ok) s_scaling = scaling_of(ch, cw, out_h, out_w);
+    __syncthreads();
     int regime = kCopy, isx = 1, isy = 1;
+    const int nbands = (out_h + band_rows - 1) / band_rows;
     if (ok) {
-        const Scaling sc = scaling_of(ch, cw, out_h, out_w);
+        const Scaling &sc = s_scaling;
         regime = sc.regime;
         isx = sc.isx;
         isy = sc.isy;
         if (regime == kArea || regime == kLinear) {
-            for (int k = threadIdx.x; k < out_w; k += blockDim.x) fill_taps(tx, k, k, regime, cw, sc.inv_x, sc.sc_x, true);
-            for (int k = threadIdx.x; k < out_h; k += blockDim.x) fill_taps(ty, k, k, regime, ch, sc.inv_y, sc.sc_y, false);
+            // x taps of every column; y taps of the rows this CTA produces (of all rows when a
+            // translation can move a band anywhere)
+            const int my_bands = rows_in_place ? (nbands - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : nbands;
+            const int band_step = rows_in_place ? (int)gridDim.x : 1, band_first = rows_in_place ? (int)blockIdx.x : 0;
+            for (int e = threadIdx.x; e < out_w + my_bands * band_rows; e += blockDim.x) {
+                if (e < out_w) {
+                    fill_taps(tx, e, e, regime, cw, sc.inv_x, sc.sc_x, true);
+                } else {
+                    const int k = e - out_w, b = k / band_rows;
+                    const int y = (band_first + b * band_step) * band_rows + (k - b * band_rows);
+                    if (y < out_h) fill_taps(ty, y, y, regime, ch, sc.inv_y, sc.sc_y, false);
+                }
+            }
         }
     }
     __syncthreads();
@@ -267,18 +300,11 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
                 o[c * chan_step] = s_lut[c * 256 + val[c]];
         }
     };
-    // With flips only (or no augmentation) nothing is ever filled and the column an output column
-    // comes from does not depend on the row: the trace is done once per column.
-    bool flips_only = true;
-    for (int k = 0; k < ops.n_ops; k++) flips_only = flips_only && ops.type[k] == kOpFlip;
     bool mirrored = false;
     if (flips_only)
         for (int k = 0; k < ops.n_ops; k++) mirrored ^= prm[4 + 2 * k] != 0;
-    bool rows_in_place = true; // no translation: output row y comes from row y of the resized crop
-    for (int k = 0; k < ops.n_ops; k++) rows_in_place = rows_in_place && ops.type[k] != kOpTranslate;
     // A CTA produces every gridDim.x-th band of its image: what was set up above (descriptor, tap
     // tables, lookup table) serves all of them.
-    const int nbands = (out_h + band_rows - 1) / band_rows;
     for (int band = blockIdx.x; band < nbands; band += gridDim.x) {
     band0 = band * band_rows;
     rows = min(band_rows, out_h - band0);
