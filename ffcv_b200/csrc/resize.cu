@@ -88,6 +88,16 @@ __device__ __forceinline__ int sat_round(float v) { return min(255, max(0, __flo
 // inside the multiplication, fma(2^23 + v, w, -2^23 * w)
 __device__ __forceinline__ float u8biased(uint32_t v) { return __uint_as_float(0x4B000000u | v); }
 
+// 16 bytes from global to shared memory without passing through registers (L2 only: each source
+// byte is staged once); copies_wait() returns when this thread's copies have landed.
+__device__ __forceinline__ void copy16_async(uint32_t dst_shared, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_shared), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_wait() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
 // Per-axis tap tables in shared memory, computed once per CTA (double-precision position
 // arithmetic as OpenCV does it, then only fp32 / integer work per pixel).
 struct TapTables {
@@ -313,7 +323,8 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
     chan_step = planar ? npix : 1;
     // The source rows this band reads are staged in shared memory first, when they fit: whole
     // 16-byte words, many in flight per thread, instead of byte loads that each wait for a first
-    // touch of their sector in L2 or HBM.  The window keeps every row at its 16-byte phase.
+    // touch of their sector in L2 or HBM (asynchronous copies, no registers in between).  The
+    // window keeps every row at its 16-byte phase.
     bool staged = false;
     int win_lo = 0;
     if (win_bytes > 0 && rows_in_place && ok && (regime == kArea || regime == kLinear)) {
@@ -334,11 +345,12 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
                 const uint8_t *p = row_ptr(win_lo + row);
                 const uint32_t phase = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 15);
                 const uint4 *g = reinterpret_cast<const uint4 *>(p - phase);
-                uint4 *d = reinterpret_cast<uint4 *>(s_win + row * pitch);
+                const uint32_t d = (uint32_t)__cvta_generic_to_shared(s_win + row * pitch);
                 const int chunks = (int)(phase + cw * 3 + 15) >> 4;
-                for (int k = lane; k < chunks; k += 32) d[k] = __ldg(g + k);
+                for (int k = lane; k < chunks; k += 32) copy16_async(d + 16u * k, g + k);
                 if (lane == 0) s_rowoff[row] = row * pitch + (int)phase;
             }
+            copies_wait();
             __syncthreads();
         }
     }
