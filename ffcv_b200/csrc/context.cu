@@ -869,7 +869,8 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
             plane_bytes += align_up(pw * ph, 16);
         }
         d.rgb_off = rgb_bytes;
-        rgb_bytes += align_up((size_t)d.dec_height * d.dec_width * 3, 16);
+        d.rgb_pitch = (uint32_t)align_up((size_t)d.dec_width * 3, 16);
+        rgb_bytes += (size_t)d.dec_height * d.rgb_pitch;
         if ((int)d.dec_height * d.dec_width > max_pixels) max_pixels = (int)d.dec_height * d.dec_width;
         {   // extent the colour kernels' grids must cover: the crop box (plus the odd edge of a
             // chroma cell) where the kernel converts only that, else the whole image

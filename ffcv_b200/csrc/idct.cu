@@ -251,10 +251,54 @@ void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32
                                                                coef, planes);
 }
 
-// 4:2:0 images: one thread per chroma sample = 2 x 2 output pixels.  The triangle filter of the
-// four pixels reads the same 3 x 3 chroma neighbourhood (image edges replicate, which is what
-// the filter's edge formulas amount to), so the neighbourhood is loaded once: ~40 instructions
-// per pixel instead of ~240.  Only the chroma cells the crop box touches are converted.
+// 16.16 fixed-point YCbCr -> RGB of libjpeg (jdcolor.c's tables written out), one pixel.
+__device__ __forceinline__ uint32_t ycc_to_rgb(int lum, int cb, int cr) {
+    cb -= 128;
+    cr -= 128;
+    const int r = lum + ((91881 * cr + 32768) >> 16);
+    const int g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
+    const int b = lum + ((116130 * cb + 32768) >> 16);
+    return (uint32_t)min(255, max(0, r)) | (uint32_t)min(255, max(0, g)) << 8 | (uint32_t)min(255, max(0, b)) << 16;
+}
+
+// Stores four RGB pixels (12 bytes, the fourth byte of each word of `px` unused) at `o`: three
+// words when the address allows and all four pixels exist, else the first `count` pixels by bytes.
+__device__ __forceinline__ void store_rgb4(uint8_t *o, const uint32_t *px, int count, bool words) {
+    if (words && count == 4) {
+        uint32_t *w = reinterpret_cast<uint32_t *>(o);
+        w[0] = px[0] | px[1] << 24;
+        w[1] = px[1] >> 8 | px[2] << 16;
+        w[2] = px[2] >> 16 | px[3] << 8;
+    } else {
+        for (int k = 0; k < count; k++) {
+            o[3 * k] = (uint8_t)px[k];
+            o[3 * k + 1] = (uint8_t)(px[k] >> 8);
+            o[3 * k + 2] = (uint8_t)(px[k] >> 16);
+        }
+    }
+}
+
+// The box of pixels to convert: the crop box when the batch has one (valid), else the image.
+__device__ __forceinline__ void convert_box(const int32_t *params, int n_params, int img, int W, int H, int &x0,
+                                            int &y0, int &x1, int &y1) {
+    x0 = 0, y0 = 0, x1 = W, y1 = H;
+    if (params) {
+        const int32_t *p = params + (size_t)img * n_params;
+        if (p[2] > 0 && p[3] > 0 && p[0] >= 0 && p[1] >= 0 && p[0] + p[2] <= H && p[1] + p[3] <= W) {
+            y0 = p[0];
+            x0 = p[1];
+            y1 = p[0] + p[2];
+            x1 = p[1] + p[3];
+        }
+    }
+}
+
+// 4:2:0 images: one thread per pair of chroma samples = 4 x 2 output pixels.  The triangle filter
+// of the eight pixels reads a 3 x 4 chroma neighbourhood (image edges replicate, which is what the
+// filter's edge formulas amount to): its vertical blends are computed once per column, the luma
+// samples arrive as one word per row and the pixels leave as three words per row (the rows of the
+// RGB scratch start on 16-byte boundaries and a thread's first pixel is a multiple of four).
+// Only the chroma cells the crop box touches are converted.
 __global__ void __launch_bounds__(256)
 color_quad_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
                   const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb,
@@ -265,55 +309,68 @@ color_quad_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict
     const int W = d.width, H = d.height;
     const int real_w = (W + 1) >> 1, real_h = (H + 1) >> 1;
     if (real_w < 3) return; // too narrow for the filter: the per-pixel kernel replicates
-    int x0 = 0, y0 = 0, x1 = W, y1 = H; // pixel box to convert
-    if (params) {
-        const int32_t *p = params + (size_t)img * n_params;
-        if (p[2] > 0 && p[3] > 0 && p[0] >= 0 && p[1] >= 0 && p[0] + p[2] <= H && p[1] + p[3] <= W) {
-            y0 = p[0];
-            x0 = p[1];
-            y1 = p[0] + p[2];
-            x1 = p[1] + p[3];
-        }
-    }
-    const int cx = (x0 >> 1) + blockIdx.x * 32 + threadIdx.x;
+    int x0, y0, x1, y1;
+    convert_box(params, n_params, img, W, H, x0, y0, x1, y1);
+    const int cx = ((x0 >> 1) & ~1) + 2 * (blockIdx.x * 32 + threadIdx.x); // even: pixel 2 * cx is a multiple of 4
     const int cy = (y0 >> 1) + blockIdx.y * 8 + threadIdx.y;
     if (cx > ((x1 - 1) >> 1) || cy > ((y1 - 1) >> 1)) return;
     const int yw = d.mcus_x * 16, cw = d.mcus_x * 8;
-    const int xl = max(cx - 1, 0), xr = min(cx + 1, real_w - 1);
+    const int xl = max(cx - 1, 0), xr = min(cx + 2, real_w - 1);
+    const bool second = cx + 1 <= real_w - 1; // the pair's second column exists
     const int yu = max(cy - 1, 0), yd = min(cy + 1, real_h - 1);
-    int cval[2][4]; // [Cb, Cr][upper-left, upper-right, lower-left, lower-right]
+    // chroma of the 4 x 2 pixels: [Cb, Cr][row][pixel]
+    int cval[2][2][4];
 #pragma unroll
     for (int k = 0; k < 2; k++) {
         const uint8_t *P = planes + d.plane_off[1 + k];
         const uint8_t *ru = P + (size_t)yu * cw, *rc = P + (size_t)cy * cw, *rd = P + (size_t)yd * cw;
-        const int cl = rc[xl], cc = rc[cx], cr = rc[xr];
-        const int ul = 3 * cl + ru[xl], uc = 3 * cc + ru[cx], ur = 3 * cr + ru[xr]; // towards the row above
-        const int dl = 3 * cl + rd[xl], dc = 3 * cc + rd[cx], dr = 3 * cr + rd[xr]; // towards the row below
-        cval[k][0] = (3 * uc + ul + 8) >> 4;
-        cval[k][1] = (3 * uc + ur + 7) >> 4;
-        cval[k][2] = (3 * dc + dl + 8) >> 4;
-        cval[k][3] = (3 * dc + dr + 7) >> 4;
+        int up[4], dn[4]; // columns cx - 1 .. cx + 2 blended towards the row above / below
+        {
+            const int c = rc[xl];
+            up[0] = 3 * c + ru[xl];
+            dn[0] = 3 * c + rd[xl];
+        }
+        {
+            const uint32_t u = *reinterpret_cast<const uint16_t *>(ru + cx), c = *reinterpret_cast<const uint16_t *>(rc + cx),
+                           w = *reinterpret_cast<const uint16_t *>(rd + cx);
+            up[1] = 3 * (int)(c & 255) + (int)(u & 255);
+            dn[1] = 3 * (int)(c & 255) + (int)(w & 255);
+            up[2] = second ? 3 * (int)(c >> 8) + (int)(u >> 8) : up[1];
+            dn[2] = second ? 3 * (int)(c >> 8) + (int)(w >> 8) : dn[1];
+        }
+        {
+            const int c = rc[xr];
+            up[3] = second ? 3 * c + ru[xr] : up[1];
+            dn[3] = second ? 3 * c + rd[xr] : dn[1];
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) { // the pair's columns
+            cval[k][0][2 * j] = (3 * up[1 + j] + up[j] + 8) >> 4;
+            cval[k][0][2 * j + 1] = (3 * up[1 + j] + up[2 + j] + 7) >> 4;
+            cval[k][1][2 * j] = (3 * dn[1 + j] + dn[j] + 8) >> 4;
+            cval[k][1][2 * j + 1] = (3 * dn[1 + j] + dn[2 + j] + 7) >> 4;
+        }
     }
     const uint8_t *Y = planes + d.plane_off[0];
     uint8_t *out = rgb + d.rgb_off;
+    const int x = 2 * cx, count = min(4, W - x);
+    const bool words = ((reinterpret_cast<uintptr_t>(out) | d.rgb_pitch) & 3) == 0;
 #pragma unroll
-    for (int q = 0; q < 4; q++) {
-        const int x = 2 * cx + (q & 1), y = 2 * cy + (q >> 1);
-        if (x >= W || y >= H) continue;
-        const int lum = Y[(size_t)y * yw + x];
-        const int cb = cval[0][q] - 128, cr = cval[1][q] - 128;
-        const int r = lum + ((91881 * cr + 32768) >> 16);
-        const int g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
-        const int b = lum + ((116130 * cb + 32768) >> 16);
-        uint8_t *o = out + ((size_t)y * W + x) * 3;
-        o[0] = (uint8_t)min(255, max(0, r));
-        o[1] = (uint8_t)min(255, max(0, g));
-        o[2] = (uint8_t)min(255, max(0, b));
+    for (int r = 0; r < 2; r++) {
+        const int y = 2 * cy + r;
+        if (y >= H) continue;
+        const uint32_t lum = *reinterpret_cast<const uint32_t *>(Y + (size_t)y * yw + x);
+        uint32_t px[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) px[q] = ycc_to_rgb((lum >> (8 * q)) & 255, cval[0][r][q], cval[1][r][q]);
+        store_rgb4(out + (size_t)y * d.rgb_pitch + (size_t)x * 3, px, count, words);
     }
 }
 
 // 4:4:4 images, and images decoded at reduced scale (whose chroma blocks were inverted to the luma
-// resolution): no upsampling, one thread per pixel of the crop box, 2-D tiles (no divisions).
+// resolution): no upsampling, one thread per four pixels of a row of the crop box (one word of each
+// plane in, three words out), every thread walking a column strip so that the grid stays small
+// for very large images.
 __global__ void __launch_bounds__(256)
 color_444_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
                  const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb,
@@ -322,32 +379,36 @@ color_444_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict_
     const ImageDesc &d = descs[img];
     if (d.host_status != 0 || d.ncomp != 3 || !(d.scale_shift != 0 || (d.hs == 1 && d.vs == 1))) return;
     const int W = d.dec_width, H = d.dec_height;
-    int x0 = 0, y0 = 0, x1 = W, y1 = H;
-    if (params) {
-        const int32_t *p = params + (size_t)img * n_params;
-        if (p[2] > 0 && p[3] > 0 && p[0] >= 0 && p[1] >= 0 && p[0] + p[2] <= H && p[1] + p[3] <= W) {
-            y0 = p[0];
-            x0 = p[1];
-            y1 = p[0] + p[2];
-            x1 = p[1] + p[3];
-        }
-    }
+    int x0, y0, x1, y1;
+    convert_box(params, n_params, img, W, H, x0, y0, x1, y1);
     const int pw = d.mcus_x * d.hs * d.bs_luma; // = the chroma planes' pitch: all planes have one resolution here
     const uint8_t *Y = planes + d.plane_off[0], *Cb = planes + d.plane_off[1], *Cr = planes + d.plane_off[2];
     uint8_t *out = rgb + d.rgb_off;
-    // every thread walks a column strip so that the grid stays small for very large images
-    const int x = x0 + blockIdx.x * 32 + threadIdx.x;
+    const int x = (x0 & ~3) + 4 * (blockIdx.x * 32 + threadIdx.x);
     if (x >= x1) return;
+    const int count = min(4, W - x);
+    // a plane's pitch is a multiple of 8 only at full scale; reduced planes may be narrower
+    const bool words_in = ((pw | (int)(d.plane_off[0] | d.plane_off[1] | d.plane_off[2])) & 3) == 0;
+    const bool words_out = ((reinterpret_cast<uintptr_t>(out) | d.rgb_pitch) & 3) == 0;
     for (int y = y0 + blockIdx.y * 8 + threadIdx.y; y < y1; y += gridDim.y * 8) {
         const size_t s = (size_t)y * pw + x;
-        const int lum = Y[s], cb = Cb[s] - 128, cr = Cr[s] - 128;
-        const int r = lum + ((91881 * cr + 32768) >> 16);
-        const int g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
-        const int b = lum + ((116130 * cb + 32768) >> 16);
-        uint8_t *o = out + ((size_t)y * W + x) * 3;
-        o[0] = (uint8_t)min(255, max(0, r));
-        o[1] = (uint8_t)min(255, max(0, g));
-        o[2] = (uint8_t)min(255, max(0, b));
+        uint32_t lum = 0, cb = 0, cr = 0;
+        if (words_in) {
+            lum = *reinterpret_cast<const uint32_t *>(Y + s);
+            cb = *reinterpret_cast<const uint32_t *>(Cb + s);
+            cr = *reinterpret_cast<const uint32_t *>(Cr + s);
+        } else {
+            for (int q = 0; q < count; q++) {
+                lum |= (uint32_t)Y[s + q] << (8 * q);
+                cb |= (uint32_t)Cb[s + q] << (8 * q);
+                cr |= (uint32_t)Cr[s + q] << (8 * q);
+            }
+        }
+        uint32_t px[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+            px[q] = ycc_to_rgb((lum >> (8 * q)) & 255, (cb >> (8 * q)) & 255, (cr >> (8 * q)) & 255);
+        store_rgb4(out + (size_t)y * d.rgb_pitch + (size_t)x * 3, px, count, words_out);
     }
 }
 
@@ -380,9 +441,10 @@ color_other_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restric
             g = lum + ((-22554 * cb - 46802 * cr + 32768) >> 16);
             b = lum + ((116130 * cb + 32768) >> 16);
         }
-        out[(size_t)i * 3 + 0] = (uint8_t)min(255, max(0, r));
-        out[(size_t)i * 3 + 1] = (uint8_t)min(255, max(0, g));
-        out[(size_t)i * 3 + 2] = (uint8_t)min(255, max(0, b));
+        uint8_t *o = out + (size_t)y * d.rgb_pitch + (size_t)x * 3;
+        o[0] = (uint8_t)min(255, max(0, r));
+        o[1] = (uint8_t)min(255, max(0, g));
+        o[2] = (uint8_t)min(255, max(0, b));
     }
 }
 
@@ -393,11 +455,11 @@ void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n
     if (n_444 > 0) {
         int gy = (max_h + 7) / 8;
         if (gy > 64) gy = 64;
-        dim3 grid((max_w + 31) / 32, gy, n_list);
+        dim3 grid(((max_w + 3) / 4 + 1 + 31) / 32, gy, n_list); // + 1: a box starts up to 3 pixels into its first group
         color_444_kernel<<<grid, dim3(32, 8), 0, stream>>>(descs, list, planes, rgb, crop_params, n_params);
     }
     if (n_quad > 0) {
-        dim3 grid(((max_w + 1) / 2 + 31) / 32, ((max_h + 1) / 2 + 7) / 8, n_list);
+        dim3 grid((((max_w + 1) / 2 + 1) / 2 + 1 + 31) / 32, ((max_h + 1) / 2 + 7) / 8, n_list); // pairs of chroma columns
         color_quad_kernel<<<grid, dim3(32, 8), 0, stream>>>(descs, list, planes, rgb, crop_params, n_params);
     }
     if (n_other > 0) {

@@ -193,7 +193,7 @@ resize_augment_kernel(const __grid_constant__ ResizeSource src, const int32_t *_
         const ImageDesc &d = src.descs[i];
         img_h = d.dec_height; // the decoded size: smaller than the stored one after a scaled decode
         img_w = d.dec_width;
-        stride = d.dec_width * 3;
+        stride = (int)d.rgb_pitch;
         if (d.mode == 1) {
             base = src.blob + d.payload_off;
             row0 = d.row0;

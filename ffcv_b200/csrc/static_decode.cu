@@ -97,6 +97,7 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
     d.height = d.dec_height = (uint16_t)height;
     d.width = d.dec_width = (uint16_t)width;
     d.bs_luma = d.bs_chroma = 8; // full scale
+    d.rgb_pitch = (uint32_t)width * 3; // the caller's buffer is packed
     d.scan_off = (uint32_t)h.scan_off;
     d.scan_len = (uint32_t)h.scan_len;
     d.ncomp = (uint8_t)h.ncomp;

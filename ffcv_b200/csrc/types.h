@@ -19,7 +19,11 @@ struct ImageDesc {
     uint16_t height, width;
     uint16_t row0, rows;   // raw: first image row present in the staged payload, number of rows
     uint16_t col0, cols;   // raw: first image column present, number of columns
-    uint32_t raw_pitch;    // raw: bytes between staged rows (>= cols * 3)
+    union {
+        uint32_t raw_pitch; // raw: bytes between staged rows (>= cols * 3)
+        uint32_t rgb_pitch; // JPEG: bytes between rows of the decoded RGB image (>= dec_width * 3; a multiple
+                            // of 16 in the batch scratch so that the colour kernels store whole words)
+    };
     // ---- JPEG only ----
     uint32_t scan_off;     // entropy-coded segment, relative to payload_off
     uint32_t scan_len;
