@@ -201,7 +201,8 @@ struct Slot {
     ffcvb_plan plan{};
     int n = 0, n_jpeg = 0, n_par = 0, n_seq = 0, max_pixels = 0, subseq_bits = 512, entropy_threads = 512;
     int n_quad = 0, n_444 = 0, n_other = 0, max_w = 0, max_h = 0;
-    uint64_t jpeg_list_off = 0, par_list_off = 0, seq_list_off = 0;
+    uint64_t jpeg_list_off = 0, par_list_off = 0, seq_list_off = 0, quad_tiles_off = 0;
+    int n_quad_tiles = 0;
     uint32_t total_blocks = 0;
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes = 0, raw_bytes = 0, jpeg_bytes = 0;
     bool staged = false;
@@ -820,6 +821,7 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     std::vector<const uint16_t *> mult_src;
     std::vector<int> huff_of_store(ctx->huff_store.size(), -1), mult_of_store(ctx->quant_store.size(), -1);
     std::vector<int32_t> jpeg_list, par_list, seq_list;
+    std::vector<uint2> quad_tiles; // (sample, tile x | tile y << 16) of the 4:2:0 colour kernel's CTAs
     size_t clean_bytes = 0, plane_bytes = 0, rgb_bytes = 0, scan_bytes_par = 0;  // scan_bytes_par: largest scan
     uint32_t total_blocks = 0;
     int max_pixels = 0, max_w = 0, max_h = 0, n_quad = 0, n_444 = 0, n_other = 0;
@@ -872,9 +874,9 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
         d.rgb_pitch = (uint32_t)align_up((size_t)d.dec_width * 3, 16);
         rgb_bytes += (size_t)d.dec_height * d.rgb_pitch;
         if ((int)d.dec_height * d.dec_width > max_pixels) max_pixels = (int)d.dec_height * d.dec_width;
+        int bw = d.dec_width, bh = d.dec_height;
         {   // extent the colour kernels' grids must cover: the crop box (plus the odd edge of a
             // chroma cell) where the kernel converts only that, else the whole image
-            int bw = d.dec_width, bh = d.dec_height;
             const bool boxed = d.ncomp == 3 && ((d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3) || (d.hs == 1 && d.vs == 1));
             if (plan->resize && boxed) {
                 const int32_t *p = params + (size_t)i * n_params;
@@ -890,9 +892,13 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
         }
         if (d.scale_shift != 0)
             n_444++; // decoded at reduced scale: all planes at one resolution, no upsampling
-        else if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3)
+        else if (d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (d.width + 1) / 2 >= 3) {
             n_quad++;
-        else if (d.ncomp == 3 && d.hs == 1 && d.vs == 1)
+            // the tiles of 64 x 8 chroma samples (one CTA each) that cover this image's box
+            const uint32_t tiles_x = (uint32_t)((((bw + 1) / 2 + 1) / 2 + 1 + 31) / 32), tiles_y = (uint32_t)(((bh + 1) / 2 + 7) / 8);
+            for (uint32_t ty = 0; ty < tiles_y; ty++)
+                for (uint32_t tx = 0; tx < tiles_x; tx++) quad_tiles.push_back(make_uint2((uint32_t)i, tx | ty << 16));
+        } else if (d.ncomp == 3 && d.hs == 1 && d.vs == 1)
             n_444++;
         else
             n_other++;
@@ -967,6 +973,8 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
         off = align_up(off + sizeof(int32_t) * par_list.size(), 16);
         s.seq_list_off = off;
         off = align_up(off + sizeof(int32_t) * seq_list.size(), 16);
+        s.quad_tiles_off = off;
+        off = align_up(off + sizeof(uint2) * quad_tiles.size(), 16);
     };
     if (!from_fd) place_tables();
     hd.params_off = off;
@@ -1083,6 +1091,8 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     if (!jpeg_list.empty()) memcpy(s.host + s.jpeg_list_off, jpeg_list.data(), 4 * jpeg_list.size());
     if (!par_list.empty()) memcpy(s.host + s.par_list_off, par_list.data(), 4 * par_list.size());
     if (!seq_list.empty()) memcpy(s.host + s.seq_list_off, seq_list.data(), 4 * seq_list.size());
+    if (!quad_tiles.empty()) memcpy(s.host + s.quad_tiles_off, quad_tiles.data(), sizeof(uint2) * quad_tiles.size());
+    s.n_quad_tiles = (int)quad_tiles.size();
 
     const auto t2 = std::chrono::steady_clock::now();
     // ---- parallel: gather the payload bytes into pinned memory
@@ -1266,7 +1276,8 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         launch_idct(descs, jl, s.n_jpeg, s.total_blocks, mult, (const int16_t *)s.coef.p,
                     (uint8_t *)s.planes.p, st);
         if (prof) CU(cudaEventRecord(s.ev[3], st));
-        launch_color(descs, jl, s.n_jpeg, s.n_quad, s.n_444, s.n_other, s.max_w, s.max_h, (const uint8_t *)s.planes.p,
+        launch_color(descs, jl, s.n_jpeg, s.n_quad, s.n_444, s.n_other, s.max_w, s.max_h,
+                     reinterpret_cast<const uint2 *>(blob + s.quad_tiles_off), s.n_quad_tiles, (const uint8_t *)s.planes.p,
                      (uint8_t *)s.rgb.p, s.plan.resize ? params : nullptr, (int)hd.n_params, st);
         if (prof) CU(cudaEventRecord(s.ev[4], st));
     } else if (prof) {

@@ -301,9 +301,21 @@ __device__ __forceinline__ void convert_box(const int32_t *params, int n_params,
 // Only the chroma cells the crop box touches are converted.
 __global__ void __launch_bounds__(256)
 color_quad_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict__ list,
-                  const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb,
+                  const uint2 *__restrict__ tiles, const uint8_t *__restrict__ planes, uint8_t *__restrict__ rgb,
                   const int32_t *__restrict__ params, int n_params) {
-    const int img = list[blockIdx.z];
+    // which sample and which tile of 64 x 8 chroma samples of its box: from the batch's tile table
+    // (one CTA per tile that exists), or, without a table, from a grid that covers the largest box
+    int img, tile_x, tile_y;
+    if (tiles) {
+        const uint2 t = tiles[blockIdx.x];
+        img = (int)t.x;
+        tile_x = (int)(t.y & 0xffff);
+        tile_y = (int)(t.y >> 16);
+    } else {
+        img = list[blockIdx.z];
+        tile_x = blockIdx.x;
+        tile_y = blockIdx.y;
+    }
     const ImageDesc &d = descs[img];
     if (d.host_status != 0 || d.ncomp != 3 || d.hs != 2 || d.vs != 2 || d.scale_shift != 0) return;
     const int W = d.width, H = d.height;
@@ -311,8 +323,8 @@ color_quad_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restrict
     if (real_w < 3) return; // too narrow for the filter: the per-pixel kernel replicates
     int x0, y0, x1, y1;
     convert_box(params, n_params, img, W, H, x0, y0, x1, y1);
-    const int cx = ((x0 >> 1) & ~1) + 2 * (blockIdx.x * 32 + threadIdx.x); // even: pixel 2 * cx is a multiple of 4
-    const int cy = (y0 >> 1) + blockIdx.y * 8 + threadIdx.y;
+    const int cx = ((x0 >> 1) & ~1) + 2 * (tile_x * 32 + threadIdx.x); // even: pixel 2 * cx is a multiple of 4
+    const int cy = (y0 >> 1) + tile_y * 8 + threadIdx.y;
     if (cx > ((x1 - 1) >> 1) || cy > ((y1 - 1) >> 1)) return;
     const int yw = d.mcus_x * 16, cw = d.mcus_x * 8;
     const int xl = max(cx - 1, 0), xr = min(cx + 2, real_w - 1);
@@ -449,7 +461,7 @@ color_other_kernel(const ImageDesc *__restrict__ descs, const int32_t *__restric
 }
 
 void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n_quad, int n_444, int n_other,
-                  int max_w, int max_h, const uint8_t *planes, uint8_t *rgb, const int32_t *crop_params,
+                  int max_w, int max_h, const uint2 *quad_tiles, int n_quad_tiles, const uint8_t *planes, uint8_t *rgb, const int32_t *crop_params,
                   int n_params, cudaStream_t stream) {
     if (n_list == 0) return;
     if (n_444 > 0) {
@@ -458,9 +470,13 @@ void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n
         dim3 grid(((max_w + 3) / 4 + 1 + 31) / 32, gy, n_list); // + 1: a box starts up to 3 pixels into its first group
         color_444_kernel<<<grid, dim3(32, 8), 0, stream>>>(descs, list, planes, rgb, crop_params, n_params);
     }
-    if (n_quad > 0) {
+    if (n_quad > 0 && quad_tiles != nullptr) {
+        if (n_quad_tiles > 0)
+            color_quad_kernel<<<n_quad_tiles, dim3(32, 8), 0, stream>>>(descs, list, quad_tiles, planes, rgb, crop_params,
+                                                                        n_params);
+    } else if (n_quad > 0) {
         dim3 grid((((max_w + 1) / 2 + 1) / 2 + 1 + 31) / 32, ((max_h + 1) / 2 + 7) / 8, n_list); // pairs of chroma columns
-        color_quad_kernel<<<grid, dim3(32, 8), 0, stream>>>(descs, list, planes, rgb, crop_params, n_params);
+        color_quad_kernel<<<grid, dim3(32, 8), 0, stream>>>(descs, list, nullptr, planes, rgb, crop_params, n_params);
     }
     if (n_other > 0) {
         int bx = (max_w * max_h + 256 * 4 - 1) / (256 * 4);

@@ -49,13 +49,16 @@ void launch_entropy_decode(const ImageDesc *descs, const int32_t *list, int n_li
 void launch_idct(const ImageDesc *descs, const int32_t *list, int n_list, uint32_t total_blocks,
                  const MultTable *mult, const int16_t *coef, uint8_t *planes, cudaStream_t stream);
 
-// Chroma upsampling (triangle filter) + YCbCr->RGB into packed h*w*3 images in `rgb`.  4:2:0
-// images (n_quad of them) go through the 2x2-quad kernel and 4:4:4 images (n_444) through a
-// per-pixel 2-D kernel, both converting only the crop box given by `crop_params` (row, col, h, w
-// per sample; nullptr = whole image); the other n_other images go through the generic kernel.  max_w / max_h bound the image sizes in the list.
+// Chroma upsampling (triangle filter) + YCbCr->RGB into h*w*3 images in `rgb` (rows rgb_pitch
+// apart).  4:2:0 images (n_quad of them) go through the quad kernel and 4:4:4 images (n_444)
+// through a 2-D kernel, both converting only the crop box given by `crop_params` (row, col, h, w
+// per sample; nullptr = whole image); the other n_other images go through the generic kernel.
+// max_w / max_h bound the boxes in the list.  quad_tiles (device; may be nullptr): one entry
+// (sample, tile x | tile y << 16) per tile of 64 x 8 chroma samples the quad kernel has to
+// convert, so that it launches exactly those CTAs instead of a grid over the largest box.
 void launch_color(const ImageDesc *descs, const int32_t *list, int n_list, int n_quad, int n_444, int n_other,
-                  int max_w, int max_h, const uint8_t *planes, uint8_t *rgb, const int32_t *crop_params,
-                  int n_params, cudaStream_t stream);
+                  int max_w, int max_h, const uint2 *quad_tiles, int n_quad_tiles, const uint8_t *planes,
+                  uint8_t *rgb, const int32_t *crop_params, int n_params, cudaStream_t stream);
 
 // Source of the fused kernel.
 struct ResizeSource {

@@ -152,8 +152,8 @@ extern "C" int ffcvb_imdecode_static(const uint8_t *jpeg_host, uint64_t jpeg_siz
                 scratch + kPlaneOff, st);
     const bool quad = d.ncomp == 3 && d.hs == 2 && d.vs == 2 && (width + 1) / 2 >= 3;
     const bool full = d.ncomp == 3 && d.hs == 1 && d.vs == 1;
-    launch_color(desc_dev, list_dev, 1, quad ? 1 : 0, full ? 1 : 0, (quad || full) ? 0 : 1, (int)width, (int)height, scratch + kPlaneOff,
-                 rgb_dev, nullptr, 0, st);
+    launch_color(desc_dev, list_dev, 1, quad ? 1 : 0, full ? 1 : 0, (quad || full) ? 0 : 1, (int)width, (int)height,
+                 nullptr, 0, scratch + kPlaneOff, rgb_dev, nullptr, 0, st);
     if (cudaGetLastError() != cudaSuccess) return reject(FFCVB_E_CUDA, "kernel launch failed");
     return FFCVB_OK;
 }
