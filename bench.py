@@ -439,17 +439,19 @@ class Bench:
         # While this process waited at the barrier its loader filled the queue of prepared batches.
         # They are consumed before the clock starts, so that the timed region begins in the steady
         # state of producer and consumer and bills only batches produced inside it.
+        # (The clock sampler starts first: spawning it takes long enough for the queue to fill again.)
+        if sampler is not None:
+            sampler.start()
         t0 = time.perf_counter()
         ahead = loader.batches_ahead + 2
         for _ in range(ahead):
             digest += consume()
         ch.cuda.synchronize()
         est = max(1e-5, (time.perf_counter() - t0) / ahead)
-        timed = max(steps, min(600, int(math.ceil(1.0 / est)))) if steps < 100 else steps
+        # at least a second's worth of steps, and several times the queue's depth
+        timed = max(steps, 6 * ahead, min(600, int(math.ceil(1.0 / est)))) if steps < 100 else steps
         if self.world > 1:  # every rank times the same number of steps
             timed = int(self.max_over_ranks([timed])[0])
-        if sampler is not None:
-            sampler.start()
         # The timed steps are taken as three consecutive segments and the median segment is the
         # result: the host side of this path (DRAM and PCIe) is shared with whatever else runs on
         # the machine, and a neighbour's burst would otherwise decide the figure.

@@ -7,6 +7,8 @@ operations that implement :meth:`Operation.fuse` becomes a :class:`FusedImagePla
 (or raw) sample bytes go to the GPU and one call of the native library produces the final tensor.
 Operations after the fused prefix run one by one through their ``generate_code`` closures.
 """
+from concurrent.futures import ThreadPoolExecutor
+
 import numpy as np
 import torch as ch
 
@@ -159,6 +161,7 @@ class FusedImageExecutor:
         self.h2d_bytes = 0
         self.launches = 0
         self.riders = []          # other fields' values for the next batch (see Graph.attach_riders)
+        self._helper = None       # one thread that draws the next batch's parameters (see __call__)
 
     def allocate(self, batch_size, slots):
         p = self.plan
@@ -191,13 +194,22 @@ class FusedImageExecutor:
         if self.riders:
             self.ctx.set_riders(slot, self.riders, n)
             self.riders = []
-        # with asynchronous staging this returns while the staging threads still copy the payloads ...
-        self.ctx.stage(slot, self.file_base_fn(), *args[:5], self.native_plan, params)
-        # ... which is when the next batch's parameters are drawn
+        # The next batch's parameters are drawn by a helper thread while this thread is inside the
+        # native calls (which release the interpreter lock): the loader thread's time per batch is
+        # what bounds the rate of the low-resolution configurations.
+        ahead = None
         if lookahead is not None:
-            self._prepared = ((epoch, batch_ix + 1, len(lookahead)), self.prepare(lookahead, epoch, batch_ix + 1))
-        dst = out[:n]
-        self.ctx.submit(slot, stream_ptr, dst.data_ptr())
+            if self._helper is None:
+                self._helper = ThreadPoolExecutor(max_workers=1, thread_name_prefix='ffcv_b200_params')
+            ahead = self._helper.submit(self.prepare, lookahead, epoch, batch_ix + 1)
+        try:
+            # with asynchronous staging this returns while the staging threads still copy the payloads
+            self.ctx.stage(slot, self.file_base_fn(), *args[:5], self.native_plan, params)
+            dst = out[:n]
+            self.ctx.submit(slot, stream_ptr, dst.data_ptr())
+        finally:
+            if ahead is not None:
+                self._prepared = ((epoch, batch_ix + 1, len(lookahead)), ahead.result())
         self.h2d_bytes = self.ctx.staged_bytes(slot)
         self.launches = self.ctx.launches(slot)
         p = self.plan
