@@ -211,6 +211,37 @@ def ncu_constants(cfg):
     return entry, stale
 
 
+def numa_placement(device_index):
+    """(memory node of the GPU, node of the first CPU this process may run on, MB of shared-memory
+    pages per node); -1 / [] where the system does not say."""
+    import glob
+    import torch
+    gpu_node, cpu_node, per_node = -1, -1, []
+    try:
+        nodes = sorted(int(os.path.basename(p)[4:]) for p in glob.glob('/sys/devices/system/node/node[0-9]*'))
+        for n in nodes:
+            mb = -1.0
+            with open(f'/sys/devices/system/node/node{n}/meminfo') as fp:
+                for line in fp:
+                    if ' Shmem:' in line:
+                        mb = int(line.split()[-2]) / 1024.0
+            per_node.append(mb)
+        first_cpu = min(os.sched_getaffinity(0))
+        for n in nodes:
+            with open(f'/sys/devices/system/node/node{n}/cpulist') as fp:
+                for part in fp.read().strip().split(','):
+                    lo, _, hi = part.partition('-')
+                    if part and int(lo) <= first_cpu <= int(hi or lo):
+                        cpu_node = n
+        props = torch.cuda.get_device_properties(device_index)
+        bdf = f'{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0'
+        with open(f'/sys/bus/pci/devices/{bdf}/numa_node') as fp:
+            gpu_node = int(fp.read().strip())
+    except Exception:  # noqa: BLE001 - a diagnostic must not take the measurement down
+        pass
+    return gpu_node, cpu_node, per_node
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
     FIELDS = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
@@ -720,6 +751,14 @@ class Bench:
                                               'total': float(r[3])},
                                  'gather_kernel_ms': float(r[4]) if r[4] >= 0 else None, 'ms_per_step': float(r[5])}
                                 for r in stats]
+            # where the bytes lie and who reads them: the host's memory nodes, how much of the
+            # memory file system's pages (the benchmark's file) each holds, and for every rank the
+            # node of its GPU and the node its threads run on
+            gpu_node, cpu_node, per_node = numa_placement(self.local)
+            placement = self.gather_ranks([gpu_node, cpu_node])
+            link['numa'] = {'shmem_mb_per_node': per_node,
+                            'gpu_node_per_rank': [int(r[0]) for r in placement],
+                            'cpu_node_per_rank': [int(r[1]) for r in placement]}
 
         configs = {}
         if self.world == 1 and not args.no_configs and not args.kernels_only and cfg == 2:
