@@ -14,9 +14,11 @@
 //   interpolation on both axes with 11-bit fixed-point weights.
 // Byte work bound by instruction issue: a few CTAs per sample, each producing every k-th band of
 // output rows; tap positions and weights are computed once per CTA into shared memory and serve all
-// its bands, source taps go through L1/L2, every band's normalised tile is assembled in shared
-// memory and leaves with coalesced 16-byte stores.  In the fractional shrinking regime a thread owns
-// an output column for a run of rows, so that the horizontal sums of a source row are shared by the
+// its bands; the source rows a band reads are staged in shared memory by asynchronous 16-byte
+// copies when they fit (taps straight from global memory otherwise); every band's normalised tile
+// is assembled in shared memory and leaves with coalesced 16-byte stores.  In the fractional
+// shrinking and the enlarging regime a thread owns an output column for a run of rows, so that
+// what a source row contributes (its horizontal sums, its interpolated values) is shared by the
 // output rows that touch it.
 #include <float.h>
 
@@ -35,9 +37,6 @@ struct AreaTaps {
     int first, n;
     float wl, wm, wr;
     bool has_l, has_r;
-    __device__ __forceinline__ float weight(int k) const {
-        return (k == 0 && has_l) ? wl : ((k == n - 1 && has_r) ? wr : wm);
-    }
 };
 
 // a / b correctly rounded, given the correctly rounded 1 / b: the product with the reciprocal is
