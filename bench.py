@@ -505,6 +505,9 @@ class Bench:
             if g is not None:
                 gather.append(g)
         loader._live_iterator.retire()
+        # the worker queued batches the loop above never consumed: their copies and kernels must
+        # be through before anybody restages their slots outside the loader's own fences
+        ch.cuda.synchronize()
         return dict(ms=float(np.median(segments)) * 3, segments=[v / (timed // 3) for v in segments], steps=timed,
                     h2d=int(np.mean(h2d)), launches=exe.launches, digest=digest,
                     stage_ms=np.mean(np.array(stage), axis=0) if stage else np.zeros(4),
@@ -760,12 +763,18 @@ class Bench:
                             'gpu_node_per_rank': [int(r[0]) for r in placement],
                             'cpu_node_per_rank': [int(r[1]) for r in placement]}
 
+        # measured here, before the side passes below: whatever happens in those, the headline
+        # line has all it needs
+        solo = self.link_peak(concurrent=False) if self.world == 1 and not args.kernels_only else None
+
         configs = {}
         if self.world == 1 and not args.no_configs and not args.kernels_only and cfg == 2:
             for c in sorted(WORKLOADS):
                 if c == cfg:
                     continue
                 st = min(args.steps, 8 if c == 4 else 20)
+                print(f'[bench] side pass: config {c}' + (' with the decode index' if self.decode_index else ''),
+                      file=sys.stderr, flush=True)
                 try:
                     r = self.measure(c, st, min(args.warmup, 3 if c == 4 else 5), full=False)
                     rl = self.roofline(r, c, clocks)
@@ -786,6 +795,8 @@ class Bench:
                 if c == 0:
                     continue  # no JPEG samples
                 st = min(args.steps, 8 if c == 4 else 20)
+                print(f'[bench] side pass: config {c}' + (' with the decode index' if self.decode_index else ''),
+                      file=sys.stderr, flush=True)
                 try:
                     r = self.measure(c, st, min(args.warmup, 3 if c == 4 else 5), full=False)
                     indexed[f'c{c}'] = {'value': r['value'], 'ms_per_step': r['ms_per_step'], 'e2e': r['e2e']['value'],
@@ -802,7 +813,6 @@ class Bench:
         roofline = self.roofline(m, cfg, clocks)
 
         if not args.kernels_only:
-            solo = self.link_peak(concurrent=False) if self.world == 1 else None
             e2e = m['e2e']
             bytes_s = e2e['h2d_bytes_per_step'] / (m['e2e_raw']['ms'] / m['e2e_raw']['steps'] * 1e-3) / 1e9
             peak_link = solo if solo is not None else link.get('concurrent_gbs_min')

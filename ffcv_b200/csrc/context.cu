@@ -599,7 +599,9 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
         }
         fd_payload_end = off;
         // room behind the payloads for what is laid out after the parse: at most 255 tables of each kind
-        const size_t tail = 255 * (sizeof(HuffTable) + sizeof(MultTable)) + 3 * (sizeof(int32_t) * (size_t)n + 16) + 256;
+        size_t tail = 255 * (sizeof(HuffTable) + sizeof(MultTable)) + 3 * (sizeof(int32_t) * (size_t)n + 16) + 256;
+        for (int i = 0; i < n; i++) // and the colour kernel's tile table: at most the tiles of whole images
+            tail += sizeof(uint2) * (size_t)((((heights[i] + 1) / 2 + 7) / 8) * ((((widths[i] + 1) / 2 + 1) / 2 + 1 + 31) / 32));
         int grc;
         if ((grc = grow_host(ctx, s.host, s.host_cap, fd_payload_end + tail))) return grc;
     }
@@ -1035,6 +1037,8 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     int rc;
     // The staging buffer is sized for the whole batch although a pinned source uses only part of
     // it: the part varies from batch to batch, and regrowing page-locked memory stalls the device.
+    if (from_fd && off + 64 > s.host_cap) // the payloads already sit in the buffer: it cannot be regrown now
+        return fail(ctx, FFCVB_E_ARG, "ffcvb_stage_batch_fd: tables and lists do not fit behind the payloads");
     if ((rc = grow_host(ctx, s.host, s.host_cap, off + 64))) return rc;
     if ((rc = grow_dev(ctx, s.blob, off + 64))) return rc;
     if ((rc = grow_dev(ctx, s.clean, clean_bytes + 64))) return rc;
@@ -1609,6 +1613,8 @@ int ffcvb_host_register(void *ptr, uint64_t bytes) {
 
 int ffcvb_host_unregister(void *ptr) {
     if (!ptr) return FFCVB_E_ARG;
+    // gather kernels and copies that still read the range must be through before it is released
+    cudaDeviceSynchronize();
     if (cudaHostUnregister(ptr) != cudaSuccess) {
         cudaGetLastError();
         return FFCVB_E_CUDA;
