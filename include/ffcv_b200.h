@@ -198,6 +198,8 @@ int ffcvb_set_staging_split(ffcvb_ctx *ctx, int cpu_share_permille);
  * mappings and files on disk are refused) and leaves no CUDA error behind.  No counterpart in
  * the reference. */
 int ffcvb_host_register(void *ptr, uint64_t bytes);
+/* Releases the page lock.  Waits for the device first (cudaDeviceSynchronize): batches submitted
+ * earlier may still be gathering payloads from the range. */
 int ffcvb_host_unregister(void *ptr);
 
 /* The share (per mille) the next batch will be staged with. */
