@@ -230,6 +230,11 @@ struct Slot {
     // the large grids other slots have queued, and the PCIe transfer overlaps their compute
     cudaStream_t gather_stream = nullptr;
     cudaEvent_t ev_begin = nullptr, ev_gather_start = nullptr, ev_gathered = nullptr;
+    // recorded behind the last work queued on the slot: staging the slot again waits for it, so a
+    // caller that forgets to fence the ring gets a stall instead of a batch whose descriptors are
+    // overwritten under its kernels
+    cudaEvent_t ev_done = nullptr;
+    bool in_flight = false;
     bool gather_timed = false; // ev_gather_start .. ev_gathered bracket the last gather of this slot
     bool timed = false; // events of the last run are valid
 };
@@ -447,6 +452,7 @@ void ffcvb_destroy(ffcvb_ctx *ctx) {
             if (e) cudaEventDestroy(e);
         if (s.gather_stream) cudaStreamDestroy(s.gather_stream);
         if (s.ev_begin) cudaEventDestroy(s.ev_begin);
+        if (s.ev_done) cudaEventDestroy(s.ev_done);
         if (s.ev_gathered) cudaEventDestroy(s.ev_gathered);
         if (s.ev_gather_start) cudaEventDestroy(s.ev_gather_start);
     }
@@ -516,6 +522,10 @@ int stage_impl(ffcvb_ctx *ctx, int slot, const Source &source, const uint64_t *p
     if (!valid_plan(plan)) return fail(ctx, FFCVB_E_ARG, "ffcvb_stage_batch: invalid plan");
     CU(cudaSetDevice(ctx->device));
     Slot &s = ctx->slots[slot];
+    if (s.in_flight) { // normally complete long ago (the caller fences the ring): returns at once
+        CU(cudaEventSynchronize(s.ev_done));
+        s.in_flight = false;
+    }
     s.staged = false;
     s.plan = *plan;
     s.n = n;
@@ -1298,6 +1308,9 @@ static int run_batch(ffcvb_ctx *ctx, Slot &s, cudaStream_t st, void *out_dev, bo
         CU(cudaEventRecord(s.ev[5], st));
         s.timed = true;
     }
+    if (!s.ev_done) CU(cudaEventCreateWithFlags(&s.ev_done, cudaEventDisableTiming));
+    CU(cudaEventRecord(s.ev_done, st));
+    s.in_flight = true;
     return FFCVB_OK;
 }
 
